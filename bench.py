@@ -1,0 +1,446 @@
+#!/usr/bin/env python
+"""Benchmark of the GeMKM/GeKMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config C5]
+
+One step = one complete GeMKM/GeKMM call (all passes) on one synthetic operand set.
+The default workload is the distributed benchmark configuration C5 (fp32 GeMKM,
+M=256, four 64x64 factors, K = 64^4 = 16.8M columns, 17 GB of X): it fits one B200,
+so the same problem is measured at 1, 2, 4 and 8 GPUs (strong scaling; at N > 1 the
+columns of X are sharded over the ranks).  With N = 1 the line also carries the
+single-GPU configurations C1-C4 under "configs".
+
+Metric: GFLOP/s with the reference library's operation count
+2*M*sum_i(K_out,i * P_i) (src/kmm/kmmalgo.h:174-184 of the reference); the count of the
+reference's test harness, which adds the epilogue (tests/testBase.h:994-1003), is
+reported as "value_harness_count".
+
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    # name: mm, dtype, M, Ps, Qs, opX, opF, alpha, beta, seed, distribution of X/Y
+    "C1": dict(mm="mkm", dt="f32", M=1024, ps=[16] * 4, qs=[16] * 4, opx="N", opf="N", alpha=1.0, beta=0.0, seed=0, dist="uniform"),
+    "C2": dict(mm="mkm", dt="f64", M=16, ps=[8] * 8, qs=[8] * 8, opx="N", opf="N", alpha=1.0, beta=0.0, seed=1, dist="uniform"),
+    "C3": dict(mm="kmm", dt="f32", M=1024, ps=[32] * 3, qs=[32] * 3, opx="T", opf="N", alpha=2.0, beta=1.0, seed=2, dist="normal"),
+    # C4: "opF = T on F1 only" cannot be said through the C API's single opFs; as in the
+    # reference's own Python wrapper the transposed factor is materialised and opFs = N.
+    "C4": dict(mm="mkm", dt="f32", M=2048, ps=[128, 128, 16], qs=[128, 128, 16], opx="N", opf="N", alpha=1.0, beta=0.0, seed=4, dist="uniform"),
+    "C5": dict(mm="mkm", dt="f32", M=256, ps=[64] * 4, qs=[64] * 4, opx="N", opf="N", alpha=1.0, beta=0.0, seed=5, dist="uniform"),
+}
+# reduced copies for quick functional runs of this script (--config C5s etc.)
+CONFIGS["C5s"] = dict(CONFIGS["C5"], M=16, ps=[64] * 3, qs=[64] * 3)
+CONFIGS["C1s"] = dict(CONFIGS["C1"], M=64)
+
+
+def flops_library(c, M=None):
+    M = c["M"] if M is None else M
+    cols = int(np.prod(c["ps"], dtype=object))
+    tot = 0
+    for p, q in reversed(list(zip(c["ps"], c["qs"]))):
+        cols = cols // p * q
+        tot += cols * p
+    return 2 * M * tot
+
+
+def flops_harness(c, M=None):
+    M = c["M"] if M is None else M
+    L = int(np.prod(c["qs"], dtype=object))
+    return flops_library(c, M) + 2 * M * (L + (2 * L if c["beta"] != 0 else 0))
+
+
+def algorithmic_bytes(c, M=None):
+    """X read once + Z written once (+ Y read when beta != 0) + factors."""
+    M = c["M"] if M is None else M
+    es = 4 if c["dt"] == "f32" else 8
+    K = int(np.prod(c["ps"], dtype=object))
+    L = int(np.prod(c["qs"], dtype=object))
+    b = M * K + M * L + (M * L if c["beta"] != 0 else 0) + sum(p * q for p, q in zip(c["ps"], c["qs"]))
+    return b * es
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for ln in open(self.path):
+                f = [t.strip() for t in ln.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out = {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                   "samples": len(sm)}
+        return out
+
+
+def make_device_operands(c, M=None, col_shard=None):
+    """Seeded operands in HBM.  Uniform operands are generated on the device by the same
+    counter-based generator the CPU oracle inputs use; normal ones come from the host."""
+    import torch
+    from fastkron_b200 import synth
+    M = c["M"] if M is None else M
+    tdt = torch.float32 if c["dt"] == "f32" else torch.float64
+    ndt = np.float32 if c["dt"] == "f32" else np.float64
+    K = int(np.prod(c["ps"], dtype=object))
+    L = int(np.prod(c["qs"], dtype=object))
+    x = torch.empty(M * K, dtype=tdt, device="cuda")
+    if c["dist"] == "normal":
+        x.copy_(torch.from_numpy(synth.normal(c["seed"], M * K, ndt)))
+    else:
+        synth.fill_uniform_cuda(x, c["seed"])
+    y = None
+    if c["beta"] != 0:
+        gen = synth.normal if c["dist"] == "normal" else synth.uniform
+        y = torch.from_numpy(gen(c["seed"] + 1000, M * L, ndt)).cuda()
+    fs = [torch.from_numpy(synth.uniform(c["seed"] + 2000 + i, p * q, ndt)).cuda()
+          for i, (p, q) in enumerate(zip(c["ps"], c["qs"]))]
+    return x, fs, y
+
+
+OPC = {"N": 1, "T": 2}
+
+
+def call(h, c, M, x, fs, z, y, t1, t2):
+    h.raw_gemm(c["mm"], "s" if c["dt"] == "f32" else "d", M, c["ps"], c["qs"], x.data_ptr(), OPC[c["opx"]],
+               [f.data_ptr() for f in fs], OPC[c["opf"]], z.data_ptr(), c["alpha"], c["beta"],
+               y.data_ptr() if y is not None else 0, t1.data_ptr(), t2.data_ptr())
+
+
+def time_config(h, c, steps, warmup, profile=False):
+    """Device-resident timing of one configuration on one GPU.  Returns a dict."""
+    import torch
+    from fastkron_b200 import lib as fk
+    M = c["M"]
+    tdt = torch.float32 if c["dt"] == "f32" else torch.float64
+    x, fs, y = make_device_operands(c)
+    ye, te = h.sizes(M, c["ps"], c["qs"])
+    z = torch.empty(ye, dtype=tdt, device="cuda")
+    t1 = torch.empty(te, dtype=tdt, device="cuda")
+    t2 = torch.empty(te, dtype=tdt, device="cuda")
+    L = fk.get()
+    L.fkbLaunchCount.restype = ctypes.c_ulonglong
+    for _ in range(warmup):
+        call(h, c, M, x, fs, z, y, t1, t2)
+    torch.cuda.synchronize()
+    if profile:
+        L.fkbSetProfiling(h.h, 1)
+    n0 = L.fkbLaunchCount()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in ev:
+        a.record()
+        call(h, c, M, x, fs, z, y, t1, t2)
+        b.record()
+    torch.cuda.synchronize()
+    launches = L.fkbLaunchCount() - n0
+    times = [a.elapsed_time(b) for a, b in ev]
+    passes = None
+    if profile:
+        ms = (ctypes.c_float * 4096)()
+        kinds = (ctypes.c_int * 4096)()
+        n = L.fkbGetPassTimes(h.h, ms, kinds, 4096)
+        L.fkbSetProfiling(h.h, 0)
+        per = n // steps if steps else 0
+        passes = []
+        for p in range(per):
+            vals = [ms[s * per + p] for s in range(steps)]
+            passes.append({"kind": ["generic", "tile", "gemm"][kinds[p]], "ms": float(np.mean(vals))})
+    total_ms = float(sum(times))
+    return {"ms_per_step": total_ms / steps, "ms_min": float(min(times)), "launches": int(launches),
+            "passes": passes, "buffers": (x, fs, y, z, t1, t2)}
+
+
+def measure_fma_peak(dt):
+    """FFMA / DFMA issue peak of this GPU from a register-only FMA chain kernel (TFLOP/s)."""
+    import torch
+    from fastkron_b200 import synth
+    synth.fill_uniform_cuda(torch.empty(16, device="cuda"), 0)     # loads the helper library
+    lib = synth._slib
+    fn = lib.fkbFmaPeakF32 if dt == "f32" else lib.fkbFmaPeakF64
+    fn.restype = ctypes.c_ulonglong
+    blocks = 148 * 8
+    out = torch.empty(blocks * 256, dtype=torch.float32 if dt == "f32" else torch.float64, device="cuda")
+    iters = 20000 if dt == "f32" else 8000
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    best = 0.0
+    for i in range(6):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        n = fn(ctypes.c_void_p(out.data_ptr()), ctypes.c_int(blocks), ctypes.c_int(iters), st)
+        b.record()
+        torch.cuda.synchronize()
+        if n and i >= 1:
+            best = max(best, 2.0 * n / (a.elapsed_time(b) * 1e-3) / 1e12)
+    return best
+
+
+def read_measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return json.load(open(p)), "measured"
+    except Exception:
+        return {"hbm_gbs": 6650.0}, "fallback"
+
+
+def cpu_sample(c, rows, reps, threads=None):
+    """Time the reference x86 backend (oracle/_ref) -- or, where that library is absent,
+    the C restatement -- on `rows` rows of configuration c with all host threads."""
+    import oracle
+    from fastkron_b200 import synth
+    ndt = np.float32 if c["dt"] == "f32" else np.float64
+    K = int(np.prod(c["ps"], dtype=object))
+    L = int(np.prod(c["qs"], dtype=object))
+    gen = synth.normal if c["dist"] == "normal" else synth.uniform
+    x = gen(c["seed"], rows * K, ndt)
+    y = gen(c["seed"] + 1000, rows * L, ndt) if c["beta"] != 0 else None
+    fs = [synth.uniform(c["seed"] + 2000 + i, p * q, ndt) for i, (p, q) in enumerate(zip(c["ps"], c["qs"]))]
+    cores = threads or os.cpu_count() or 1
+    best = None
+    if oracle.ref_available():
+        kind = "reference"
+        ref = oracle.RefLib(threads=cores)
+        z = np.zeros(rows * L, dtype=ndt)
+        _, te = ref.sizes(rows, c["ps"], c["qs"])
+        temps = (np.zeros(te, dtype=ndt), np.zeros(te, dtype=ndt))
+        for i in range(reps + 1):
+            t0 = time.perf_counter()
+            ref.gekmm(c["mm"], x, fs, c["ps"], c["qs"], rows, c["opx"], c["opf"], c["alpha"], c["beta"], y, z=z, temps=temps)
+            dt = time.perf_counter() - t0
+            if i >= 1:
+                best = dt if best is None else min(best, dt)
+        ref.close()
+    else:
+        kind = "port"
+        os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+        for i in range(reps + 1):
+            t0 = time.perf_counter()
+            oracle.port_gekmm(c["mm"], x, fs, c["ps"], c["qs"], rows, c["opx"], c["opf"], c["alpha"], c["beta"], y)
+            dt = time.perf_counter() - t0
+            if i >= 1:
+                best = dt if best is None else min(best, dt)
+    return {"value": flops_library(c, rows) / best / 1e9, "unit": "GFLOP/s", "cores": cores, "kind": kind,
+            "sample": "%d of %d rows of %s, best of %d after 1 warm-up, %.3f s per call" % (rows, c["M"], c["name"], reps, best),
+            "seconds": best}
+
+
+def cpu_rows_for(c):
+    """Rows of the workload that keep one reference call at a few seconds of CPU work
+    (and under the reference's 32-bit element count, src/kmm/matrix.h:112)."""
+    per_row = flops_library(c, 1)
+    rows = max(1, min(c["M"], int(150e9 // per_row)))     # ~150 GFLOP per call
+    K = int(np.prod(c["ps"], dtype=object))
+    while rows > 1 and rows * K >= (1 << 31):
+        rows //= 2
+    return rows
+
+
+def run_reference(args):
+    c = dict(CONFIGS[args.config], name=args.config)
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = cpu_rows_for(c)
+    t0 = time.perf_counter()
+    res = cpu_sample(c, rows, reps=max(args.steps, 1))
+    out = {
+        "impl": "reference", "metric": "GeMKM/GeKMM GFLOP/s", "value": res["value"], "unit": "GFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["seconds"] * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": c["dt"], "data": "synthetic",
+        "config": workload_desc(c, args.gpus),
+        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": res["value"], "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t0,
+    }
+    print(json.dumps(out))
+
+
+def workload_desc(c, gpus):
+    return {"workload": "%s: %s %s M=%d factors=%s opX=%s opF=%s alpha=%g beta=%g seed=%d" % (
+        c["name"], "sge" if c["dt"] == "f32" else "dge", c["mm"], c["M"],
+        "x".join("%dx%d" % (p, q) for p, q in zip(c["ps"], c["qs"])), c["opx"], c["opf"], c["alpha"], c["beta"], c["seed"]),
+        "gpus": gpus, "sharding": "none" if gpus == 1 else "X columns over %d ranks" % gpus,
+        "l2": "operands exceed L2 (no flush needed)" if algorithmic_bytes(c) > 2 * 126e6 else "operands fit L2; not flushed"}
+
+
+def run_single(args):
+    import torch
+    import fastkron_b200
+    from fastkron_b200 import lib as fk
+    c = dict(CONFIGS[args.config], name=args.config)
+    torch.cuda.set_device(0)
+    h = fastkron_b200.FastKron()
+    peaks, peak_src = read_measured_peaks()
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    r = time_config(h, c, args.steps, args.warmup, profile=True)
+    clocks = sampler.stop()
+    flops = flops_library(c)
+    value = flops / (r["ms_per_step"] * 1e-3) / 1e9
+
+    # ---- roofline of the dominant kernel ------------------------------------------
+    fma_peak = measure_fma_peak(c["dt"])
+    passes = r["passes"] or []
+    dom = max(passes, key=lambda p: p["ms"]) if passes else None
+    es = 4 if c["dt"] == "f32" else 8
+    K = int(np.prod(c["ps"], dtype=object))
+    pass_bytes = 2 * c["M"] * K * es                     # one pass reads and writes the matrix once
+    roof = None
+    if dom is not None:
+        # per-launch work of a pass: every pass of these configs moves the whole matrix
+        # once; its flops are the call's flops split in proportion to the factors it applies
+        idx = passes.index(dom)
+        n_launch = len(passes)
+        dom_flops = flops / n_launch if len(set(c["ps"])) == 1 else None
+        hbm_ach = pass_bytes / (dom["ms"] * 1e-3) / 1e9
+        roof_hbm = {"bound": "hbm", "achieved": hbm_ach, "peak": peaks.get("hbm_gbs"), "unit": "GB/s",
+                    "frac": hbm_ach / peaks.get("hbm_gbs"), "traffic": None, "peak_source": peak_src,
+                    "kernel": dom["kind"], "pass_index": idx, "launch_ms": dom["ms"]}
+        roof = roof_hbm
+        if dom_flops is not None and fma_peak > 0:
+            fp_ach = dom_flops / (dom["ms"] * 1e-3) / 1e12
+            roof_fp = {"bound": "fp32_simt" if c["dt"] == "f32" else "fp64_simt", "achieved": fp_ach, "peak": fma_peak,
+                       "unit": "TFLOP/s", "frac": fp_ach / fma_peak, "traffic": None,
+                       "peak_source": "FMA-chain probe in this run", "kernel": dom["kind"], "pass_index": idx,
+                       "launch_ms": dom["ms"]}
+            if roof_fp["frac"] > roof_hbm["frac"]:
+                roof = dict(roof_fp, other=roof_hbm)
+            else:
+                roof = dict(roof_hbm, other=roof_fp)
+
+    # ---- end to end through the C ABI with host buffers -------------------------------
+    x, fs, y, z, t1, t2 = r["buffers"]
+    e2e = None
+    try:
+        hx = torch.empty(x.numel(), dtype=x.dtype, pin_memory=True)
+        hz = torch.empty(z.numel(), dtype=z.dtype, pin_memory=True)
+        hx.copy_(x)
+        torch.cuda.synchronize()
+        e2e_steps = max(1, min(args.steps, 3))
+        for it in range(1 + e2e_steps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            x.copy_(hx, non_blocking=True)
+            call(h, c, c["M"], x, fs, z, y, t1, t2)
+            hz.copy_(z, non_blocking=True)
+            b.record()
+            torch.cuda.synchronize()
+            if it == 0:
+                tt = []
+            else:
+                tt.append(a.elapsed_time(b))
+        e2e_ms = float(np.mean(tt))
+        e2e = {"value": flops / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "h2d_bytes_per_step": x.numel() * es,
+               "d2h_bytes_per_step": z.numel() * es, "ms_per_step": e2e_ms, "steps": e2e_steps}
+        del hx, hz
+    except RuntimeError as ex:      # pinned allocation failed
+        e2e = {"value": None, "unit": "GFLOP/s", "error": str(ex)[:200]}
+    del x, fs, y, z, t1, t2, r["buffers"]
+    torch.cuda.empty_cache()
+
+    # ---- the other single-GPU configurations ---------------------------------------------
+    extra = {}
+    if not args.no_extra and args.config == "C5":
+        for name in ("C1", "C2", "C3", "C4"):
+            cc = dict(CONFIGS[name], name=name)
+            rr = time_config(h, cc, max(3, args.steps), max(3, args.warmup), profile=True)
+            del rr["buffers"]
+            torch.cuda.empty_cache()
+            fl = flops_library(cc)
+            sec = rr["ms_per_step"] * 1e-3
+            extra[name] = {"gflops": fl / sec / 1e9, "gflops_harness_count": flops_harness(cc) / sec / 1e9,
+                           "ms_per_step": rr["ms_per_step"], "algorithmic_gbs": algorithmic_bytes(cc) / sec / 1e9,
+                           "hbm_frac_algorithmic": algorithmic_bytes(cc) / sec / 1e9 / peaks.get("hbm_gbs"),
+                           "passes": rr["passes"], "launches_per_step": rr["launches"] // max(3, args.steps)}
+
+    cpu = None
+    if not args.no_cpu:
+        cpu = cpu_sample(c, cpu_rows_for(c), reps=2)
+        cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    out = {
+        "metric": "GeMKM/GeKMM GFLOP/s", "value": value, "unit": "GFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": c["dt"], "data": "synthetic", "config": workload_desc(c, 1),
+        "value_harness_count": flops_harness(c) / (r["ms_per_step"] * 1e-3) / 1e9,
+        "gpu_launches": r["launches"], "passes": passes, "clocks": clocks, "roofline": roof, "e2e": e2e,
+        "cpu_baseline": cpu, "fma_peak_tflops": fma_peak, "configs": extra,
+    }
+    print(json.dumps(out))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="C5", choices=sorted(CONFIGS))
+    ap.add_argument("--no-extra", action="store_true", help="skip the C1-C4 side measurements")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        return run_reference(args)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1 or args.gpus > 1:
+        from fastkron_b200 import mg_bench
+        return mg_bench.run(args, CONFIGS, globals())
+    return run_single(args)
+
+
+if __name__ == "__main__":
+    main()

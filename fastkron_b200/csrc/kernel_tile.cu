@@ -1,0 +1,36 @@
+// Dispatcher of the shared-memory tile kernels (instantiated in
+// kernel_tile_{f32,f64}_{narrow,wide}.cu).
+#include "kernels.h"
+#include "tile_table.h"
+
+namespace fkb {
+
+template <typename T, bool WIDE>
+fastKronError launchTileTW(const Pass& ps, const LaunchCtx& cx);
+extern template fastKronError launchTileTW<float, false>(const Pass&, const LaunchCtx&);
+extern template fastKronError launchTileTW<float, true>(const Pass&, const LaunchCtx&);
+extern template fastKronError launchTileTW<double, false>(const Pass&, const LaunchCtx&);
+extern template fastKronError launchTileTW<double, true>(const Pass&, const LaunchCtx&);
+
+bool tileSupported(DType dt, uint32_t P, int nf, int tileB) {
+  (void)dt;
+  return tileInTable(P, nf, tileB > 1);
+}
+
+fastKronError launchTile(const Pass& ps, const LaunchCtx& cx) {
+  // The kernel assumes dense row-major [chunks][G][B] on both sides, unit
+  // trailing stride, equal square factors and 16-byte aligned operands.
+  const size_t es = dtypeSize(cx.dt);
+  const bool wide = ps.B > 1;
+  if (ps.xsB != 1 || ps.zsB != 1) return fastKronKernelNotFound;
+  for (int k = 0; k < ps.nf; k++)
+    if (ps.P[k] != ps.P[0] || ps.Q[k] != ps.P[0]) return fastKronKernelNotFound;
+  const uint64_t W = 128 / es;
+  if (wide && ps.B % W != 0) return fastKronKernelNotFound;
+  if (((uintptr_t)cx.src | (uintptr_t)cx.dst | (uintptr_t)cx.Y) & 15) return fastKronKernelNotFound;
+  if (cx.dt == DType::F32)
+    return wide ? launchTileTW<float, true>(ps, cx) : launchTileTW<float, false>(ps, cx);
+  return wide ? launchTileTW<double, true>(ps, cx) : launchTileTW<double, false>(ps, cx);
+}
+
+}  // namespace fkb

@@ -1,0 +1,329 @@
+// Shared-memory tile kernel for small square power-of-two factors.
+//
+// One pass contracts NF consecutive tensor modes of size P in place:
+//   [chunks][G = P^NF][B]  ->  same shape,   chunks = M*A.
+// A CTA stages a super-tile of R sub-tiles in shared memory, applies the NF
+// factors one after the other without leaving the SM, and streams the result
+// out with 128-bit stores.  A sub-tile is one [G] block (narrow, B == 1) or a
+// [G][W] slab with W = 128 bytes of trailing elements (wide, B > 1).
+//
+// Inside a step every thread owns whole fibres (the P inputs and P outputs of
+// one contraction), so a step is read-all / compute / write-all per thread and
+// needs no barrier except between steps; the tile is updated in place.
+//
+// Shared-memory addressing.  Logical tile index i lives at phys(i): the 16-byte
+// chunk index inside each 128-byte line is XOR-ed with a 3-bit fold of the line
+// number.  phys is linear over XOR, and because P, W and the strides are powers
+// of two the index of (fibre, p) is fibreBase | p*S, hence
+//   phys(fibreBase + p*S) = phys(fibreBase) ^ phys(p*S)
+// with the second term a compile-time constant in the unrolled p loop.  The fold
+// makes both the contiguous-fibre step (stride 1) and the strided steps free of
+// bank conflicts for 128-bit accesses.
+//
+// The arithmetic of each contraction is the reference's: for every output the
+// products are accumulated over p ascending (src/kernels/cuda/mma.cuh:1-15),
+// factors applied from the last of the group to the first
+// (src/kmm/kmmalgo.cpp:172-214).
+#pragma once
+
+#include "kernels.h"
+
+#include <cmath>
+
+namespace fkb {
+
+template <typename T>
+struct TileArgs {
+  const T* X; T* Z; const T* Y;
+  const T* F[kMaxGroup];
+  long long fsP, fsQ;
+  unsigned long long B;              // trailing extent in elements
+  unsigned long long tilesPerChunk;  // B / W (1 for narrow)
+  unsigned long long numSub;         // chunks * tilesPerChunk
+  int R;                             // sub-tiles per super-tile
+  T alpha, beta;
+  int epilogue;
+};
+
+constexpr int kTileThreads = 128;
+constexpr int kTileMaxR = 64;
+
+__host__ __device__ constexpr int ipow(int b, int e) { return e == 0 ? 1 : b * ipow(b, e - 1); }
+
+template <typename T>
+__host__ __device__ constexpr unsigned physIdx(unsigned idx) {
+  constexpr int LB = (sizeof(T) == 4) ? 5 : 4;   // log2(elements per 128-byte line)
+  constexpr int VB = (sizeof(T) == 4) ? 2 : 1;   // log2(elements per 16-byte chunk)
+  const unsigned line = idx >> LB;
+  const unsigned h = (line ^ (line >> 3) ^ (line >> 6) ^ (line >> 9)) & 7u;
+  return idx ^ (h << VB);
+}
+
+template <typename T>
+struct alignas(16) Vec16 {
+  static constexpr int N = 16 / sizeof(T);
+  T v[N];
+};
+
+__device__ __forceinline__ void cpAsync16(void* smemDst, const void* gmemSrc) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smemDst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmemSrc) : "memory");
+}
+__device__ __forceinline__ void cpAsyncWaitAll() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+}
+
+// Compiler-only ordering point: keeps the fully unrolled loops from hoisting every
+// shared-memory load of a step to its top (which costs hundreds of registers).
+__host__ __device__ __forceinline__ void schedFence() {
+#ifdef __CUDA_ARCH__
+  asm volatile("" ::: "memory");
+#endif
+}
+
+// ---- one contraction step over a tile of E elements, mode stride S ----------
+
+// Strided fibres, S >= VEC: a thread owns VEC neighbouring fibres per group and
+// U groups at a time; every access is one 128-bit shared-memory transaction.
+template <typename T, int P, int S, int THREADS>
+__host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const T* __restrict__ Fs, int E, int tid) {
+  constexpr int VEC = Vec16<T>::N;
+  constexpr int U = (16 / P) > 1 ? (16 / P) : 1;
+  constexpr int FV = P < VEC ? P : VEC;
+  using V = Vec16<T>;
+  const int nvg = E / (P * VEC);
+  for (int vg0 = tid; vg0 < nvg; vg0 += THREADS * U) {
+    unsigned pb[U];
+    bool ok[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      int vg = vg0 + u * THREADS;
+      ok[u] = vg < nvg;
+      if (!ok[u]) vg = vg0;
+      const unsigned lo = (unsigned)vg % (S / VEC);
+      const unsigned hi = (unsigned)vg / (S / VEC);
+      pb[u] = physIdx<T>(hi * (unsigned)(S * P) + lo * VEC);
+    }
+    T acc[U][VEC][P];
+#pragma unroll
+    for (int u = 0; u < U; u++)
+#pragma unroll
+      for (int k = 0; k < VEC; k++)
+#pragma unroll
+        for (int q = 0; q < P; q++) acc[u][k][q] = T(0);
+
+#pragma unroll
+    for (int p = 0; p < P; p++) {
+      V xv[U];
+#pragma unroll
+      for (int u = 0; u < U; u++)
+        xv[u] = *reinterpret_cast<const V*>(tile + (pb[u] ^ physIdx<T>((unsigned)(p * S))));
+#pragma unroll
+      for (int q0 = 0; q0 < P; q0 += FV) {
+        T f[FV];
+        if (FV == VEC) {
+          const V fv = *reinterpret_cast<const V*>(Fs + p * P + q0);
+#pragma unroll
+          for (int i = 0; i < FV; i++) f[i] = fv.v[i];
+        } else {
+#pragma unroll
+          for (int i = 0; i < FV; i++) f[i] = Fs[p * P + q0 + i];
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++)
+#pragma unroll
+          for (int k = 0; k < VEC; k++)
+#pragma unroll
+            for (int i = 0; i < FV; i++) acc[u][k][q0 + i] = fma(xv[u].v[k], f[i], acc[u][k][q0 + i]);
+      }
+      schedFence();
+    }
+#pragma unroll
+    for (int q = 0; q < P; q++) {
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        V ov;
+#pragma unroll
+        for (int k = 0; k < VEC; k++) ov.v[k] = acc[u][k][q];
+        if (ok[u]) *reinterpret_cast<V*>(tile + (pb[u] ^ physIdx<T>((unsigned)(q * S)))) = ov;
+      }
+    }
+  }
+}
+
+// Contiguous fibres (S == 1, P >= VEC): a thread owns NFIB whole fibres, reads
+// and writes them as 128-bit pieces along p / q.
+template <typename T, int P, int THREADS>
+__host__ __device__ __forceinline__ void stepContig(T* __restrict__ tile, const T* __restrict__ Fs, int E, int tid) {
+  constexpr int VEC = Vec16<T>::N;
+  constexpr int U = (16 / P) > 1 ? (16 / P) : 1;
+  constexpr int NFIB = U * VEC;
+  using V = Vec16<T>;
+  const int nfib = E / P;
+  for (int f0 = tid; f0 < nfib; f0 += THREADS * NFIB) {
+    unsigned pb[NFIB];
+    bool ok[NFIB];
+#pragma unroll
+    for (int k = 0; k < NFIB; k++) {
+      int f = f0 + k * THREADS;
+      ok[k] = f < nfib;
+      if (!ok[k]) f = f0;
+      pb[k] = physIdx<T>((unsigned)f * P);
+    }
+    T acc[NFIB][P];
+#pragma unroll
+    for (int k = 0; k < NFIB; k++)
+#pragma unroll
+      for (int q = 0; q < P; q++) acc[k][q] = T(0);
+
+#pragma unroll
+    for (int p0 = 0; p0 < P; p0 += VEC) {
+      V xv[NFIB];
+#pragma unroll
+      for (int k = 0; k < NFIB; k++)
+        xv[k] = *reinterpret_cast<const V*>(tile + (pb[k] ^ physIdx<T>((unsigned)p0)));
+#pragma unroll
+      for (int pp = 0; pp < VEC; pp++) {
+#pragma unroll
+        for (int q0 = 0; q0 < P; q0 += VEC) {
+          const V fv = *reinterpret_cast<const V*>(Fs + (p0 + pp) * P + q0);
+#pragma unroll
+          for (int k = 0; k < NFIB; k++)
+#pragma unroll
+            for (int i = 0; i < VEC; i++) acc[k][q0 + i] = fma(xv[k].v[pp], fv.v[i], acc[k][q0 + i]);
+        }
+        schedFence();
+      }
+    }
+#pragma unroll
+    for (int q0 = 0; q0 < P; q0 += VEC) {
+#pragma unroll
+      for (int k = 0; k < NFIB; k++) {
+        V ov;
+#pragma unroll
+        for (int i = 0; i < VEC; i++) ov.v[i] = acc[k][q0 + i];
+        if (ok[k]) *reinterpret_cast<V*>(tile + (pb[k] ^ physIdx<T>((unsigned)q0))) = ov;
+      }
+    }
+  }
+}
+
+// Any stride, any P: one fibre per thread with scalar accesses.  Only reached
+// for the few shapes the vector steps cannot express (P or S below one 16-byte
+// chunk).
+template <typename T, int P, int S, int THREADS>
+__host__ __device__ __forceinline__ void stepScalar(T* __restrict__ tile, const T* __restrict__ Fs, int E, int tid) {
+  const int nfib = E / P;
+  for (int f = tid; f < nfib; f += THREADS) {
+    const unsigned lo = (unsigned)f % S;
+    const unsigned hi = (unsigned)f / S;
+    const unsigned base = hi * (unsigned)(S * P) + lo;
+    T x[P], o[P];
+#pragma unroll
+    for (int p = 0; p < P; p++) x[p] = tile[physIdx<T>(base + (unsigned)(p * S))];
+#pragma unroll
+    for (int q = 0; q < P; q++) {
+      T acc = T(0);
+#pragma unroll
+      for (int p = 0; p < P; p++) acc = fma(x[p], Fs[p * P + q], acc);
+      o[q] = acc;
+    }
+#pragma unroll
+    for (int q = 0; q < P; q++) tile[physIdx<T>(base + (unsigned)(q * S))] = o[q];
+  }
+}
+
+template <typename T, int P, int S, int THREADS>
+__host__ __device__ __forceinline__ void stepDispatch(T* tile, const T* Fs, int E, int tid) {
+  constexpr int VEC = Vec16<T>::N;
+  if constexpr (S >= VEC) {
+    stepStrided<T, P, S, THREADS>(tile, Fs, E, tid);
+  } else if constexpr (S == 1 && P >= VEC) {
+    stepContig<T, P, THREADS>(tile, Fs, E, tid);
+  } else {
+    stepScalar<T, P, S, THREADS>(tile, Fs, E, tid);
+  }
+}
+
+// Apply factors J, J-1, ..., 0 of the group (J = NF-1 first).
+template <typename T, int P, int NF, int BT, int THREADS, int J>
+struct StepChain {
+  static __device__ __forceinline__ void run(T* tile, const T* Fs, int E) {
+    constexpr int S = ipow(P, NF - 1 - J) * BT;
+    stepDispatch<T, P, S, THREADS>(tile, Fs + J * P * P, E, (int)threadIdx.x);
+    __syncthreads();
+    StepChain<T, P, NF, BT, THREADS, J - 1>::run(tile, Fs, E);
+  }
+};
+template <typename T, int P, int NF, int BT, int THREADS>
+struct StepChain<T, P, NF, BT, THREADS, -1> {
+  static __device__ __forceinline__ void run(T*, const T*, int) {}
+};
+
+template <typename T, int P, int NF, bool WIDE>
+__global__ void __launch_bounds__(kTileThreads) tilePassKernel(const TileArgs<T> a) {
+  constexpr int THREADS = kTileThreads;
+  constexpr int VEC = Vec16<T>::N;
+  constexpr int BT = WIDE ? (int)(128 / sizeof(T)) : 1;
+  constexpr int G = ipow(P, NF);
+  constexpr int SUB = G * BT;
+  using V = Vec16<T>;
+
+  extern __shared__ __align__(1024) unsigned char smemRaw[];
+  T* tile = reinterpret_cast<T*>(smemRaw);
+  T* Fs = tile + (size_t)a.R * SUB;
+  unsigned long long* bases = reinterpret_cast<unsigned long long*>(Fs + NF * P * P);
+
+  // factors -> shared memory as [k][p][q]
+  for (int i = threadIdx.x; i < NF * P * P; i += THREADS) {
+    const int k = i / (P * P), p = (i / P) % P, q = i % P;
+    Fs[i] = a.F[k][(long long)p * a.fsP + (long long)q * a.fsQ];
+  }
+
+  const unsigned long long R = (unsigned long long)a.R;
+  for (unsigned long long st0 = (unsigned long long)blockIdx.x * R; st0 < a.numSub;
+       st0 += (unsigned long long)gridDim.x * R) {
+    const unsigned long long left = a.numSub - st0;
+    const int nsub = left < R ? (int)left : (int)R;
+    if ((int)threadIdx.x < nsub) {
+      const unsigned long long st = st0 + threadIdx.x;
+      const unsigned long long chunk = st / a.tilesPerChunk;
+      const unsigned long long bt = st % a.tilesPerChunk;
+      bases[threadIdx.x] = chunk * (unsigned long long)G * a.B + bt * (unsigned long long)BT;
+    }
+    __syncthreads();
+
+    const int E = nsub * SUB;
+    const int nvec = E / VEC;
+    for (int v = threadIdx.x; v < nvec; v += THREADS) {
+      const unsigned idx = (unsigned)v * VEC;
+      const unsigned r = idx / SUB, w = idx % SUB;
+      const unsigned long long goff = bases[r] + (unsigned long long)(w / BT) * a.B + (w % BT);
+      cpAsync16(tile + physIdx<T>(idx), a.X + goff);
+    }
+    cpAsyncWaitAll();
+    __syncthreads();
+
+    StepChain<T, P, NF, BT, THREADS, NF - 1>::run(tile, Fs, E);
+
+    for (int v = threadIdx.x; v < nvec; v += THREADS) {
+      const unsigned idx = (unsigned)v * VEC;
+      const unsigned r = idx / SUB, w = idx % SUB;
+      const unsigned long long goff = bases[r] + (unsigned long long)(w / BT) * a.B + (w % BT);
+      V o = *reinterpret_cast<const V*>(tile + physIdx<T>(idx));
+      if (a.epilogue) {
+#pragma unroll
+        for (int i = 0; i < VEC; i++) o.v[i] = a.alpha * o.v[i];
+        if (a.beta != T(0) && a.Y != nullptr) {
+          const V y = *reinterpret_cast<const V*>(a.Y + goff);
+#pragma unroll
+          for (int i = 0; i < VEC; i++) o.v[i] = fma(a.beta, y.v[i], o.v[i]);
+        }
+      }
+      *reinterpret_cast<V*>(a.Z + goff) = o;
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace fkb

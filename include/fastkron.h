@@ -1,0 +1,234 @@
+/*
+ * fastkron.h -- C ABI of the B200-native GeMKM / GeKMM engine.
+ *
+ * The declarations below reproduce, symbol for symbol and argument for argument,
+ * the public interface of abhijangda/fastkron (include/fastkron.h:27-628 in that
+ * project) so that programs and bindings written against it link against this
+ * library without change.  Enum values are part of the ABI and are identical.
+ * The implementation behind the interface is new: a host planner plus
+ * hand-written sm_100a kernels (see fastkron_b200/csrc).
+ *
+ * Operation
+ *   GeMKM:  Z = alpha * op(X) * (op(F1) (x) ... (x) op(FN)) + beta * Y
+ *           op(X) is M x K (K = prod Ps), op(Fi) is Ps[i] x Qs[i],
+ *           Y and Z are M x L (L = prod Qs), everything row-major.
+ *   GeKMM:  Z = alpha * (op(F1) (x) ... (x) op(FN)) * op(X) + beta * Y
+ *           op(Fi) is Qs[i] x Ps[i], op(X) is K x M, Y and Z are L x M.
+ *   fastKronOp_T on an operand means its buffer holds the transpose of the
+ *   row-major operand (i.e. the operand stored column-major).
+ *
+ * Only the CUDA backend exists in this library.  Requests for any other
+ * backend are answered with an error code; nothing is computed on the host.
+ */
+#pragma once
+
+#include <stdint.h>
+#include <stddef.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+/* Caller-side convenience: abort the program on a non-success return code.
+ * (reference: include/fastkron.h:9-17) */
+#define FastKronCHECK(cmd) do {                                   \
+  fastKronError e_ = (cmd);                                       \
+  if (e_ != fastKronSuccess) {                                    \
+    printf("Failed: FastKron error %s:%d at %s:%d \n",            \
+           fastKronGetErrorString(e_), (int)e_, __FILE__, __LINE__); \
+    exit(EXIT_FAILURE);                                           \
+  }                                                               \
+} while (0)
+
+/* reference: include/fastkron.h:27-30 */
+enum fastKronOp {
+  fastKronOp_N = 1,   /* buffer is the row-major operand               */
+  fastKronOp_T = 2    /* buffer is the transpose of the row-major operand */
+};
+
+/* reference: include/fastkron.h:42-48 */
+enum fastKronBackend {
+  fastKronBackend_NONE = 1 << 0,
+  fastKronBackend_X86  = 1 << 1,
+  fastKronBackend_ARM  = 1 << 2,
+  fastKronBackend_CUDA = 1 << 3,
+  fastKronBackend_HIP  = 1 << 4
+};
+
+/* reference: include/fastkron.h:57-61 */
+enum fastKronOptions {
+  fastKronOptionsNone      = 1 << 0,
+  fastKronOptionsUseFusion = 1 << 1,  /* allow several factors per kernel     */
+  fastKronOptionsTune      = 1 << 2   /* time candidate plans on first use    */
+};
+
+/* reference: include/fastkron.h:74-82 */
+enum fastKronError {
+  fastKronSuccess             = 0,
+  fastKronBackendNotAvailable = 1,
+  fastKronInvalidMemoryAccess = 2,
+  fastKronKernelNotFound      = 3,
+  fastKronInvalidArgument     = 4,
+  fastKronInvalidKMMProblem   = 5,
+  fastKronOtherError          = 6
+};
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef __cplusplus
+typedef enum fastKronOp fastKronOp;
+typedef enum fastKronBackend fastKronBackend;
+typedef enum fastKronError fastKronError;
+#endif
+
+/* Opaque library context.  A handle is used by one host thread at a time. */
+typedef void* fastKronHandle;
+
+/* ---- library information (reference: include/fastkron.h:95-121) ---------- */
+const char* fastKronVersion();
+const char* fastKronCUDAArchs();
+const char* fastKronGetErrorString(fastKronError err);
+/* Bitwise OR of the fastKronBackend values compiled into this library. */
+uint32_t    fastKronGetBackends();
+
+/* ---- handle life cycle (reference: include/fastkron.h:123-204) ----------- */
+/* Create a handle for the OR-ed `backends`.  A backend that this library does
+ * not contain yields fastKronInvalidArgument (the handle is still written). */
+fastKronError fastKronInit(fastKronHandle* handle, uint32_t backends);
+fastKronError fastKronInitAllBackends(fastKronHandle* handle);
+fastKronError fastKronSetOptions(fastKronHandle handle, uint32_t options);
+void          fastKronDestroy(fastKronHandle handle);
+/* `ptrToStream` points to a cudaStream_t; all later work is enqueued there. */
+fastKronError fastKronInitCUDA(fastKronHandle handle, void* ptrToStream);
+fastKronError fastKronInitHIP(fastKronHandle handle, void* ptrToStream);
+fastKronError fastKronInitX86(fastKronHandle handle);
+fastKronError fastKronSetStream(fastKronHandle handle, fastKronBackend backend,
+                                void* ptrToStream);
+
+/* ---- sizes (reference: include/fastkron.h:249-251) ------------------------ */
+/* Number of elements of the result and of EACH temporary buffer. */
+fastKronError gekmmSizes(fastKronHandle handle, uint32_t M, uint32_t N,
+                         uint32_t Ps[], uint32_t Qs[],
+                         size_t* yElems, size_t* tmpElems);
+
+/* ---- GeMKM (reference: include/fastkron.h:284-296) ------------------------
+ * Fs is a HOST array of N device pointers.  temp1 must not be NULL.  temp2 may
+ * be NULL unless Z aliases Y or Z is smaller than a temporary; with temp2 NULL
+ * the library uses Z itself as its second scratch buffer.  X and Fs are never
+ * written.  The call enqueues work on the handle's stream and returns. */
+fastKronError sgemkm(fastKronHandle handle, fastKronBackend backend,
+                     uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
+                     const float* X, fastKronOp opX,
+                     const float* const Fs[], fastKronOp opFs,
+                     float* Z, float alpha, float beta,
+                     const float* Y, float* temp1, float* temp2);
+fastKronError dgemkm(fastKronHandle handle, fastKronBackend backend,
+                     uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
+                     const double* X, fastKronOp opX,
+                     const double* const Fs[], fastKronOp opFs,
+                     double* Z, double alpha, double beta,
+                     const double* Y, double* temp1, double* temp2);
+
+/* ---- GeKMM (reference: include/fastkron.h:329-341); note Qs before Ps ----- */
+fastKronError sgekmm(fastKronHandle handle, fastKronBackend backend,
+                     uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
+                     const float* const Fs[], fastKronOp opFs,
+                     const float* X, fastKronOp opX,
+                     float* Z, float alpha, float beta,
+                     const float* Y, float* temp1, float* temp2);
+fastKronError dgekmm(fastKronHandle handle, fastKronBackend backend,
+                     uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
+                     const double* const Fs[], fastKronOp opFs,
+                     const double* X, fastKronOp opX,
+                     double* Z, double alpha, double beta,
+                     const double* Y, double* temp1, double* temp2);
+
+/* ---- strided-batched GeMKM / GeKMM (reference: include/fastkron.h:384-449) -
+ * Batch b uses X + b*strideX, Fs[i] + b*strideF[i], Z + b*strideZ,
+ * Y + b*strideY (strides in elements; 0 shares the operand across the batch).
+ * Each temporary holds batchCount * tmpElems elements. */
+fastKronError sgemkmStridedBatched(fastKronHandle handle, fastKronBackend backend,
+                                   uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
+                                   const float* X, fastKronOp opX, uint64_t strideX,
+                                   const float* const Fs[], fastKronOp opFs, uint64_t strideF[],
+                                   float* Z, uint64_t strideZ, float alpha, float beta,
+                                   uint32_t batchCount, const float* Y, uint64_t strideY,
+                                   float* temp1, float* temp2);
+fastKronError dgemkmStridedBatched(fastKronHandle handle, fastKronBackend backend,
+                                   uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
+                                   const double* X, fastKronOp opX, uint64_t strideX,
+                                   const double* const Fs[], fastKronOp opFs, uint64_t strideF[],
+                                   double* Z, uint64_t strideZ, double alpha, double beta,
+                                   uint32_t batchCount, const double* Y, uint64_t strideY,
+                                   double* temp1, double* temp2);
+fastKronError sgekmmStridedBatched(fastKronHandle handle, fastKronBackend backend,
+                                   uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
+                                   const float* const Fs[], fastKronOp opFs, uint64_t strideF[],
+                                   const float* X, fastKronOp opX, uint64_t strideX,
+                                   float* Z, uint64_t strideZ, float alpha, float beta,
+                                   uint32_t batchCount, const float* Y, uint64_t strideY,
+                                   float* temp1, float* temp2);
+fastKronError dgekmmStridedBatched(fastKronHandle handle, fastKronBackend backend,
+                                   uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
+                                   const double* const Fs[], fastKronOp opFs, uint64_t strideF[],
+                                   const double* X, fastKronOp opX, uint64_t strideX,
+                                   double* Z, uint64_t strideZ, double alpha, double beta,
+                                   uint32_t batchCount, const double* Y, uint64_t strideY,
+                                   double* temp1, double* temp2);
+
+/* ---- forward variants keeping every intermediate
+ *      (reference: include/fastkron.h:470-628) --------------------------------
+ * alpha = 1, beta = 0.  Intermediates[i-1] receives the matrix obtained after
+ * the factors N-1 .. i have been applied (i = N-1 .. 1), in the reference's
+ * sliced-multiply column order; its element count is intermediateElems[i-1]. */
+fastKronError gekmmSizesForward(fastKronHandle handle, uint32_t M, uint32_t N,
+                                uint32_t Ps[], uint32_t Qs[],
+                                size_t* yElems, size_t* intermediateElems);
+fastKronError smkmForward(fastKronHandle handle, fastKronBackend backend,
+                          uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
+                          const float* X, fastKronOp opX,
+                          const float* const Fs[], fastKronOp opFs,
+                          float* Z, float* Intermediates[]);
+fastKronError dmkmForward(fastKronHandle handle, fastKronBackend backend,
+                          uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
+                          const double* X, fastKronOp opX,
+                          const double* const Fs[], fastKronOp opFs,
+                          double* Z, double* Intermediates[]);
+fastKronError skmmForward(fastKronHandle handle, fastKronBackend backend,
+                          uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
+                          const float* const Fs[], fastKronOp opFs,
+                          const float* X, fastKronOp opX,
+                          float* Z, float* Intermediates[]);
+fastKronError dkmmForward(fastKronHandle handle, fastKronBackend backend,
+                          uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
+                          const double* const Fs[], fastKronOp opFs,
+                          const double* X, fastKronOp opX,
+                          double* Z, double* Intermediates[]);
+fastKronError smkmForwardStridedBatched(fastKronHandle handle, fastKronBackend backend,
+                                        uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
+                                        const float* X, fastKronOp opX, uint64_t strideX,
+                                        const float* const Fs[], fastKronOp opFs, uint64_t strideF[],
+                                        float* Z, uint64_t strideZ, uint32_t batchCount,
+                                        float* Intermediates[], uint64_t strideIntermediates[]);
+fastKronError dmkmForwardStridedBatched(fastKronHandle handle, fastKronBackend backend,
+                                        uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
+                                        const double* X, fastKronOp opX, uint64_t strideX,
+                                        const double* const Fs[], fastKronOp opFs, uint64_t strideF[],
+                                        double* Z, uint64_t strideZ, uint32_t batchCount,
+                                        double* Intermediates[], uint64_t strideIntermediates[]);
+fastKronError skmmForwardStridedBatched(fastKronHandle handle, fastKronBackend backend,
+                                        uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
+                                        const float* const Fs[], fastKronOp opFs, uint64_t strideF[],
+                                        const float* X, fastKronOp opX, uint64_t strideX,
+                                        float* Z, uint64_t strideZ, uint32_t batchCount,
+                                        float* Intermediates[], uint64_t strideIntermediates[]);
+fastKronError dkmmForwardStridedBatched(fastKronHandle handle, fastKronBackend backend,
+                                        uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
+                                        const double* const Fs[], fastKronOp opFs, uint64_t strideF[],
+                                        const double* X, fastKronOp opX, uint64_t strideX,
+                                        double* Z, uint64_t strideZ, uint32_t batchCount,
+                                        double* Intermediates[], uint64_t strideIntermediates[]);
+
+#ifdef __cplusplus
+}
+#endif
