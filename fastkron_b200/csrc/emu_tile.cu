@@ -66,8 +66,7 @@ static int runOne(int R, unsigned long long chunks, unsigned long long Bmul) {
     std::vector<int> written(E, 0);
     for (int v = 0; v < nvec; v++) {
       const unsigned idx = (unsigned)v * VEC;
-      const unsigned r = idx / SUB, w = idx % SUB;
-      const unsigned long long goff = bases[r] + (unsigned long long)(w / BT) * B + (w % BT);
+      const unsigned long long goff = tileGlobalOffset<WIDE, SUB, BT>(bases.data(), st0 * G, idx, B);
       const unsigned ph = physIdx<T>(idx);
       for (int i = 0; i < VEC; i++) { tile[ph + i] = X[goff + i]; written[ph + i]++; }
     }
@@ -75,8 +74,7 @@ static int runOne(int R, unsigned long long chunks, unsigned long long Bmul) {
     HostChain<T, P, NF, BT, NF - 1>::run(tile.data(), Fs.data(), E);
     for (int v = 0; v < nvec; v++) {
       const unsigned idx = (unsigned)v * VEC;
-      const unsigned r = idx / SUB, w = idx % SUB;
-      const unsigned long long goff = bases[r] + (unsigned long long)(w / BT) * B + (w % BT);
+      const unsigned long long goff = tileGlobalOffset<WIDE, SUB, BT>(bases.data(), st0 * G, idx, B);
       const unsigned ph = physIdx<T>(idx);
       for (int i = 0; i < VEC; i++) Z[goff + i] = tile[ph + i];
     }

@@ -1,0 +1,27 @@
+// Which large-factor (GEMM-style) kernels exist; shared by the planner and the
+// launcher.  One entry per (element type, P, Q); TJ is the tile width along the
+// trailing index.
+#pragma once
+
+#include <stdint.h>
+#include "fk_common.h"
+
+namespace fkb {
+
+inline int gemmTileJ(DType dt) { return dt == DType::F32 ? 256 : 128; }
+
+inline bool gemmShapeInTable(DType dt, uint32_t P, uint32_t Q) {
+  if (dt == DType::F32) return (P == 64 && Q == 64) || (P == 128 && Q == 128);
+  return P == 64 && Q == 64;
+}
+
+// B is the trailing extent of the dense row-major view [chunks][P][B].
+inline bool gemmEligible(DType dt, uint32_t P, uint32_t Q, uint64_t B) {
+  if (!gemmShapeInTable(dt, P, Q)) return false;
+  const uint64_t vec = 16 / dtypeSize(dt), TJ = (uint64_t)gemmTileJ(dt);
+  if (B == 1) return true;
+  if (B % vec != 0) return false;
+  return (B % TJ == 0) || (TJ % B == 0);
+}
+
+}  // namespace fkb

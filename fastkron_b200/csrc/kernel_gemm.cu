@@ -1,7 +1,62 @@
-// Placeholder until the large-factor kernel lands: reports "no kernel" so the
-// engine falls back to the generic pass.
-#include "kernels.h"
+// Host launcher of the large-factor kernels (kernel_gemm.cuh).
+#include "kernel_gemm.cuh"
+#include "gemm_table.h"
+
 namespace fkb {
-bool gemmSupported(DType, uint32_t, uint32_t, uint64_t) { return false; }
-fastKronError launchGemm(const Pass&, const LaunchCtx&) { return fastKronKernelNotFound; }
+
+bool gemmSupported(DType dt, uint32_t P, uint32_t Q, uint64_t B) { return gemmEligible(dt, P, Q, B); }
+
+template <typename T, int P, int Q, int TJ, int PC, int STAGES, int MQ, int MJ, bool XT>
+static fastKronError launchGemmOne(const Pass& ps, const LaunchCtx& cx, int mode) {
+  using C = GemmCfg<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT>;
+  GemmArgs<T> a;
+  a.X = (const T*)cx.src; a.Z = (T*)cx.dst; a.Y = (const T*)cx.Y; a.F = (const T*)cx.F[0];
+  a.fsP = cx.fsP; a.fsQ = cx.fsQ;
+  a.numChunks = ps.M * ps.A;
+  a.B = ps.B;
+  a.mode = mode;
+  a.tilesPerChunk = 1;
+  if (mode == 0) { a.tilesPerChunk = ps.B / TJ; a.numTiles = a.numChunks * a.tilesPerChunk; }
+  else if (mode == 1) { const unsigned long long per = TJ / ps.B; a.numTiles = (a.numChunks + per - 1) / per; }
+  else { a.numTiles = (a.numChunks + TJ - 1) / TJ; }
+  a.alpha = (T)cx.alpha; a.beta = (T)cx.beta; a.epilogue = ps.epilogue ? 1 : 0;
+  if (a.numTiles == 0) return fastKronSuccess;
+
+  auto kern = gemmPassKernel<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT>;
+  static int ctasPerSm = 0;
+  if (ctasPerSm == 0) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+    if (e != cudaSuccess) return cudaToFk(e);
+    int n = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, C::THREADS, C::SMEM);
+    if (e != cudaSuccess || n < 1) return e != cudaSuccess ? cudaToFk(e) : fastKronKernelNotFound;
+    ctasPerSm = n;
+  }
+  unsigned long long grid = (unsigned long long)cx.smCount * ctasPerSm;
+  if (grid > a.numTiles) grid = a.numTiles;
+  kern<<<(unsigned)grid, C::THREADS, C::SMEM, cx.stream>>>(a);
+  return cudaToFk(cudaGetLastError());
 }
+
+template <typename T, int P, int Q, int TJ, int PC, int MQ, int MJ>
+static fastKronError launchGemmShape(const Pass& ps, const LaunchCtx& cx) {
+  if (ps.B == 1) return launchGemmOne<T, P, Q, TJ, PC, 2, MQ, MJ, true>(ps, cx, 2);
+  return launchGemmOne<T, P, Q, TJ, PC, 3, MQ, MJ, false>(ps, cx, ps.B % TJ == 0 ? 0 : 1);
+}
+
+fastKronError launchGemm(const Pass& ps, const LaunchCtx& cx) {
+  if (ps.nf != 1 || ps.xsB != 1 || ps.zsB != 1) return fastKronKernelNotFound;
+  const uint32_t P = ps.P[0], Q = ps.Q[0];
+  if (!gemmEligible(cx.dt, P, Q, ps.B)) return fastKronKernelNotFound;
+  if (((uintptr_t)cx.src | (uintptr_t)cx.dst | (uintptr_t)cx.Y) & 15) return fastKronKernelNotFound;
+  if (cx.fsQ == 1 && (((uintptr_t)cx.F[0]) & 15)) return fastKronKernelNotFound;
+  if (cx.dt == DType::F32) {
+    if (P == 64 && Q == 64) return launchGemmShape<float, 64, 64, 256, 32, 8, 8>(ps, cx);
+    if (P == 128 && Q == 128) return launchGemmShape<float, 128, 128, 256, 32, 8, 8>(ps, cx);
+  } else {
+    if (P == 64 && Q == 64) return launchGemmShape<double, 64, 64, 128, 32, 8, 4>(ps, cx);
+  }
+  return fastKronKernelNotFound;
+}
+
+}  // namespace fkb

@@ -260,6 +260,20 @@ struct StepChain<T, P, NF, BT, THREADS, -1> {
   static __device__ __forceinline__ void run(T*, const T*, int) {}
 };
 
+// Global element offset of tile index idx.  Narrow super-tiles are one contiguous run
+// starting at `contigBase`; wide ones look up the base of their sub-tile.
+template <bool WIDE, int SUB, int BT>
+__host__ __device__ __forceinline__ unsigned long long tileGlobalOffset(const unsigned long long* bases,
+                                                                        unsigned long long contigBase,
+                                                                        unsigned idx, unsigned long long B) {
+  if constexpr (!WIDE) {
+    return contigBase + idx;
+  } else {
+    const unsigned r = idx / SUB, w = idx % SUB;
+    return bases[r] + (unsigned long long)(w / BT) * B + (w % BT);
+  }
+}
+
 template <typename T, int P, int NF, bool WIDE>
 __global__ void __launch_bounds__(kTileThreads) tilePassKernel(const TileArgs<T> a) {
   constexpr int THREADS = kTileThreads;
@@ -285,7 +299,7 @@ __global__ void __launch_bounds__(kTileThreads) tilePassKernel(const TileArgs<T>
        st0 += (unsigned long long)gridDim.x * R) {
     const unsigned long long left = a.numSub - st0;
     const int nsub = left < R ? (int)left : (int)R;
-    if ((int)threadIdx.x < nsub) {
+    if (WIDE && (int)threadIdx.x < nsub) {
       const unsigned long long st = st0 + threadIdx.x;
       const unsigned long long chunk = st / a.tilesPerChunk;
       const unsigned long long bt = st % a.tilesPerChunk;
@@ -297,8 +311,7 @@ __global__ void __launch_bounds__(kTileThreads) tilePassKernel(const TileArgs<T>
     const int nvec = E / VEC;
     for (int v = threadIdx.x; v < nvec; v += THREADS) {
       const unsigned idx = (unsigned)v * VEC;
-      const unsigned r = idx / SUB, w = idx % SUB;
-      const unsigned long long goff = bases[r] + (unsigned long long)(w / BT) * a.B + (w % BT);
+      const unsigned long long goff = tileGlobalOffset<WIDE, SUB, BT>(bases, st0 * G, idx, a.B);
       cpAsync16(tile + physIdx<T>(idx), a.X + goff);
     }
     cpAsyncWaitAll();
@@ -308,8 +321,7 @@ __global__ void __launch_bounds__(kTileThreads) tilePassKernel(const TileArgs<T>
 
     for (int v = threadIdx.x; v < nvec; v += THREADS) {
       const unsigned idx = (unsigned)v * VEC;
-      const unsigned r = idx / SUB, w = idx % SUB;
-      const unsigned long long goff = bases[r] + (unsigned long long)(w / BT) * a.B + (w % BT);
+      const unsigned long long goff = tileGlobalOffset<WIDE, SUB, BT>(bases, st0 * G, idx, a.B);
       V o = *reinterpret_cast<const V*>(tile + physIdx<T>(idx));
       if (a.epilogue) {
 #pragma unroll

@@ -30,7 +30,7 @@ static fastKronError launchTileOne(const Pass& ps, const LaunchCtx& cx) {
   const size_t target = (P == 32 ? 64 : 32) * 1024;
   long long R = ps.tileR > 1 ? ps.tileR : (long long)(target / (SUB * es));
   if (R < 1) R = 1;
-  if (R > kTileMaxR) R = kTileMaxR;
+  if (WIDE && R > kTileMaxR) R = kTileMaxR;      // wide sub-tiles keep a table of bases
   while (R > 1 && (a.numSub + R - 1) / R < (unsigned long long)cx.smCount * 4) R >>= 1;
   a.R = (int)R;
 

@@ -18,6 +18,7 @@
 
 #include "fk_common.h"
 #include "tile_table.h"
+#include "gemm_table.h"
 
 #include <sstream>
 
@@ -131,6 +132,12 @@ fastKronError makePlan(const Problem& pr, const PlanOptions& opt, Plan* out) {
         }
       }
 
+      if (ps.kind == KernelKind::Generic && !opt.forceGeneric && inRow == outRow && opt.align >= 16) {
+        // large factors: register-blocked contraction, one factor per pass
+        const uint64_t Bg = inRow ? B : B * pr.M;
+        if (gemmEligible(pr.dt, P, Q, Bg)) ps.kind = KernelKind::Gemm;
+      }
+
       const int f0 = i - nf + 1;
       uint64_t Pg = 1, Qg = 1;
       for (int k = 0; k < nf; k++) { ps.P[k] = pr.P[f0 + k]; ps.Q[k] = pr.Q[f0 + k]; Pg *= ps.P[k]; Qg *= ps.Q[k]; }
@@ -140,7 +147,7 @@ fastKronError makePlan(const Problem& pr, const PlanOptions& opt, Plan* out) {
       ps.f0 = f0; ps.nf = nf; ps.M = pr.M; ps.A = A; ps.B = B;
       ps.xsM = cur.ms; ps.xsB = cur.cs; ps.xsG = (int64_t)B * cur.cs; ps.xsA = (int64_t)(Pg * B) * cur.cs;
       ps.zsM = nxt.ms; ps.zsB = nxt.cs; ps.zsG = (int64_t)B * nxt.cs; ps.zsA = (int64_t)(Qg * B) * nxt.cs;
-      if (ps.kind == KernelKind::Tile && !inRow) {
+      if (ps.kind != KernelKind::Generic && !inRow) {
         // folded view: [1][A][G][B*M], unit stride along the folded index
         ps.M = 1; ps.B = B * pr.M;
         ps.xsM = 0; ps.zsM = 0;

@@ -85,6 +85,36 @@ def test_fused_tile_kernels(h, c):
     assert cases.row_rel_err(z, oracle_z(c, x, fs, y), c["mm"]) <= cases.TOL[c["dt"]]
 
 
+GEMM_CASES = [
+    cases.case("mkm", "f32", 1, [64] * 3, [64] * 3, seed=700),
+    cases.case("mkm", "f32", 5, [64] * 3, [64] * 3, "N", "N", 2.0, 1.0, seed=701),
+    cases.case("mkm", "f32", 37, [64], [64], seed=702),
+    cases.case("mkm", "f32", 3, [64, 64], [64, 64], "N", "T", 1.0, 0.0, seed=703),
+    cases.case("mkm", "f32", 300, [64, 64], [64, 64], seed=704),
+    cases.case("mkm", "f32", 3, [128, 128], [128, 128], "N", "N", 2.0, 1.0, seed=705),
+    cases.case("mkm", "f32", 2, [128, 128, 16], [128, 128, 16], seed=706),
+    cases.case("mkm", "f32", 9, [128], [128], "N", "T", 1.0, 0.0, seed=707),
+    cases.case("mkm", "f64", 5, [64, 64], [64, 64], "N", "N", 2.0, 1.0, seed=708),
+    cases.case("mkm", "f64", 1, [64] * 3, [64] * 3, seed=709),
+    cases.case("kmm", "f32", 8, [64, 64], [64, 64], "N", "N", 2.0, 1.0, seed=710),
+    cases.case("kmm", "f32", 64, [64, 64], [64, 64], "N", "T", 1.0, 0.0, seed=711),
+    cases.case("kmm", "f32", 4, [128, 128], [128, 128], seed=712),
+    cases.case("kmm", "f64", 2, [64, 64], [64, 64], "T", "N", 1.0, 0.0, seed=713),
+    cases.case("mkm", "f32", 2, [16, 64, 8, 64], [16, 64, 8, 64], seed=714),
+    cases.case("mkm", "f32", 4, [64, 16, 64], [64, 16, 64], "T", "N", 1.0, 0.0, seed=715),
+]
+
+
+@pytest.mark.parametrize("c", GEMM_CASES, ids=cases.case_id)
+def test_large_factor_kernels(h, c):
+    """64x64 / 128x128 factors: the register-blocked kernels in all three tile modes
+    (contiguous contraction index, short and long trailing extents, ragged last tile)."""
+    import gpu_util
+    x, fs, y = cases.operands(c)
+    z = gpu_util.run_case(h, c, x=x, fs=fs, y=y)
+    assert cases.row_rel_err(z, oracle_z(c, x, fs, y), c["mm"]) <= cases.TOL[c["dt"]]
+
+
 def test_fusion_off_matches_fusion_on(h):
     import gpu_util
     from fastkron_b200 import lib as fk
