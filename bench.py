@@ -45,6 +45,7 @@ CONFIGS = {
 # reduced copies for quick functional runs of this script (--config C5s etc.)
 CONFIGS["C5s"] = dict(CONFIGS["C5"], M=16, ps=[64] * 3, qs=[64] * 3)
 CONFIGS["C1s"] = dict(CONFIGS["C1"], M=64)
+CONFIGS["C5m"] = dict(CONFIGS["C5"], M=256, ps=[64] * 3, qs=[64] * 3)      # 268 MB operand: profiling size
 
 
 def flops_library(c, M=None):

@@ -8,7 +8,7 @@
 
 namespace fkb {
 
-inline int gemmTileJ(DType dt) { return dt == DType::F32 ? 256 : 128; }
+inline int gemmTileJ(DType) { return 128; }
 
 inline bool gemmShapeInTable(DType dt, uint32_t P, uint32_t Q) {
   if (dt == DType::F32) return (P == 64 && Q == 64) || (P == 128 && Q == 128);

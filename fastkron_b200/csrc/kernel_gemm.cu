@@ -6,7 +6,7 @@ namespace fkb {
 
 bool gemmSupported(DType dt, uint32_t P, uint32_t Q, uint64_t B) { return gemmEligible(dt, P, Q, B); }
 
-template <typename T, int P, int Q, int TJ, int PC, int STAGES, int MQ, int MJ, bool XT>
+template <typename T, int P, int Q, int TJ, int PC, int STAGES, int MQ, int MJ, bool XT, int UNR, int MINB>
 static fastKronError launchGemmOne(const Pass& ps, const LaunchCtx& cx, int mode) {
   using C = GemmCfg<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT>;
   GemmArgs<T> a;
@@ -21,8 +21,9 @@ static fastKronError launchGemmOne(const Pass& ps, const LaunchCtx& cx, int mode
   else { a.numTiles = (a.numChunks + TJ - 1) / TJ; }
   a.alpha = (T)cx.alpha; a.beta = (T)cx.beta; a.epilogue = ps.epilogue ? 1 : 0;
   if (a.numTiles == 0) return fastKronSuccess;
+  if (a.numTiles >= (1ull << 31) / C::NCH) return fastKronKernelNotFound;   // 32-bit tile counters
 
-  auto kern = gemmPassKernel<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT>;
+  auto kern = gemmPassKernel<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT, UNR, MINB>;
   static int ctasPerSm = 0;
   if (ctasPerSm == 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
@@ -38,23 +39,35 @@ static fastKronError launchGemmOne(const Pass& ps, const LaunchCtx& cx, int mode
   return cudaToFk(cudaGetLastError());
 }
 
-template <typename T, int P, int Q, int TJ, int PC, int MQ, int MJ>
-static fastKronError launchGemmShape(const Pass& ps, const LaunchCtx& cx) {
-  if (ps.B == 1) return launchGemmOne<T, P, Q, TJ, PC, 2, MQ, MJ, true>(ps, cx, 2);
-  return launchGemmOne<T, P, Q, TJ, PC, 3, MQ, MJ, false>(ps, cx, ps.B % TJ == 0 ? 0 : 1);
-}
-
+// Tile shapes per factor size.  They come from a sweep on B200 (variants that spill
+// or hold fewer than two CTAs per SM lose 10-15%): fp32 64x64 runs 128-thread CTAs,
+// three per SM; fp32 128x128 keeps the 64 KB factor resident and gives each thread a
+// 16x8 block so that two CTAs still fit.
 fastKronError launchGemm(const Pass& ps, const LaunchCtx& cx) {
   if (ps.nf != 1 || ps.xsB != 1 || ps.zsB != 1) return fastKronKernelNotFound;
   const uint32_t P = ps.P[0], Q = ps.Q[0];
   if (!gemmEligible(cx.dt, P, Q, ps.B)) return fastKronKernelNotFound;
   if (((uintptr_t)cx.src | (uintptr_t)cx.dst | (uintptr_t)cx.Y) & 15) return fastKronKernelNotFound;
   if (cx.fsQ == 1 && (((uintptr_t)cx.F[0]) & 15)) return fastKronKernelNotFound;
+  const bool xt = ps.B == 1;
   if (cx.dt == DType::F32) {
-    if (P == 64 && Q == 64) return launchGemmShape<float, 64, 64, 256, 32, 8, 8>(ps, cx);
-    if (P == 128 && Q == 128) return launchGemmShape<float, 128, 128, 256, 32, 8, 8>(ps, cx);
+    constexpr int TJ = 128;
+    const int mode = xt ? 2 : (ps.B % TJ == 0 ? 0 : 1);
+    if (P == 64 && Q == 64) {
+      if (xt) return launchGemmOne<float, 64, 64, TJ, 32, 3, 8, 8, true, 8, 3>(ps, cx, mode);
+      return launchGemmOne<float, 64, 64, TJ, 32, 3, 8, 8, false, 8, 3>(ps, cx, mode);
+    }
+    if (P == 128 && Q == 128) {
+      if (xt) return launchGemmOne<float, 128, 128, TJ, 32, 2, 8, 8, true, 8, 1>(ps, cx, mode);
+      return launchGemmOne<float, 128, 128, TJ, 16, 3, 16, 8, false, 8, 2>(ps, cx, mode);
+    }
   } else {
-    if (P == 64 && Q == 64) return launchGemmShape<double, 64, 64, 128, 32, 8, 4>(ps, cx);
+    constexpr int TJ = 128;
+    const int mode = xt ? 2 : (ps.B % TJ == 0 ? 0 : 1);
+    if (P == 64 && Q == 64) {
+      if (xt) return launchGemmOne<double, 64, 64, TJ, 32, 2, 8, 4, true, 8, 1>(ps, cx, mode);
+      return launchGemmOne<double, 64, 64, TJ, 32, 3, 8, 4, false, 8, 1>(ps, cx, mode);
+    }
   }
   return fastKronKernelNotFound;
 }

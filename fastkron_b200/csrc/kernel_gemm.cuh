@@ -37,11 +37,6 @@ struct GemmArgs {
   int epilogue;
 };
 
-__device__ __forceinline__ void cpAsync16Zfill(void* smemDst, const void* gmemSrc, bool valid) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(smemDst);
-  const int n = valid ? 16 : 0;
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmemSrc), "r"(n) : "memory");
-}
 __device__ __forceinline__ void cpAsyncCommit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cpAsyncWait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
@@ -60,8 +55,8 @@ struct GemmCfg {
   static_assert(MQ % VEC == 0 && MJ % VEC == 0 && PC % VEC == 0, "vector shape");
 };
 
-template <typename T, int P, int Q, int TJ, int PC, int STAGES, int MQ, int MJ, bool XT>
-__global__ void __launch_bounds__((Q / MQ) * (TJ / MJ), ((Q / MQ) * (TJ / MJ) <= 256 ? 2 : 1))
+template <typename T, int P, int Q, int TJ, int PC, int STAGES, int MQ, int MJ, bool XT, int UNR = 8, int MINB = 0>
+__global__ void __launch_bounds__((Q / MQ) * (TJ / MJ), (MINB > 0 ? MINB : ((Q / MQ) * (TJ / MJ) <= 256 ? 2 : 1)))
 gemmPassKernel(const GemmArgs<T> a) {
   using C = GemmCfg<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT>;
   using V = Vec16<T>;
@@ -70,7 +65,7 @@ gemmPassKernel(const GemmArgs<T> a) {
   constexpr int JS = TJ / NGJ;         // stride between a thread's j groups (non-XT)
   constexpr int JT = TJ / MJ;          // stride between a thread's j's (XT)
 
-  extern __shared__ __align__(16) unsigned char smemRaw[];
+  extern __shared__ __align__(1024) unsigned char smemRaw[];
   T* Fs = reinterpret_cast<T*>(smemRaw);
   T* stages = Fs + P * Q;
 
@@ -92,43 +87,66 @@ gemmPassKernel(const GemmArgs<T> a) {
     }
   }
 
-  const unsigned long long first = blockIdx.x, step = gridDim.x;
-  const unsigned long long myTiles = first < a.numTiles ? (a.numTiles - first + step - 1) / step : 0;
-  const unsigned long long total = myTiles * C::NCH;
+  const unsigned first = blockIdx.x, step = gridDim.x;
+  const unsigned numTiles = (unsigned)a.numTiles;        // the launcher keeps this below 2^31
+  const unsigned myTiles = first < numTiles ? (numTiles - first + step - 1) / step : 0;
+  const unsigned total = myTiles * C::NCH;
   const unsigned long long PB = (unsigned long long)P * a.B, QB = (unsigned long long)Q * a.B;
+  const unsigned tpc = (unsigned)a.tilesPerChunk;        // mode 0
+  const unsigned cpt = a.mode == 1 ? (unsigned)(TJ / a.B) : (unsigned)TJ;   // chunks per tile, modes 1/2
 
-  auto issue = [&](unsigned long long s) {
-    const unsigned long long t = first + (s / C::NCH) * step;
-    const int c = (int)(s % C::NCH);
-    T* st = stages + (size_t)(s % STAGES) * C::STAGE_ELEMS;
+  // Per-thread constants of the stage loads.  A stage is filled by THREADS threads
+  // taking 16-byte vectors in order, so a thread keeps one column position and walks
+  // rows: all divisions happen here, once.
+  constexpr int VPR = XT ? PC / VEC : TJ / VEC;          // vectors per stage row
+  constexpr int RPP = THREADS / VPR;                     // rows covered per sweep of the CTA
+  constexpr int NLD = (XT ? TJ : PC) / RPP;              // loads per thread per stage
+  static_assert(THREADS % VPR == 0 && (XT ? TJ : PC) % RPP == 0, "stage load shape");
+  const int ldCol = (tid % VPR) * VEC;                   // j (non-XT) or p offset (XT)
+  const int ldRow = tid / VPR;                           // first p row (non-XT) or first j (XT)
+  unsigned long long ldOff = 0;                          // global offset of (ldRow, ldCol) in a tile
+  unsigned ldChunk = 0;                                  // chunk of the tile the column lies in (mode 1)
+  if constexpr (!XT) {
+    if (a.mode == 0) ldOff = (unsigned long long)ldRow * a.B + ldCol;
+    else { ldChunk = (unsigned)(ldCol / a.B); ldOff = ldChunk * PB + (unsigned long long)ldRow * a.B + ldCol % a.B; }
+  } else {
+    ldOff = (unsigned long long)ldRow * P + ldCol;
+  }
+  const unsigned long long ldStep = XT ? (unsigned long long)RPP * P : (unsigned long long)RPP * a.B;
+  T* const ldSmem = stages + (XT ? ldRow * (PC + C::PAD) + ldCol : ldRow * TJ + ldCol);
+  constexpr int ldSmemStep = XT ? RPP * (PC + C::PAD) : RPP * TJ;
+
+  // issue state: walks (tile, chunk) pairs in order
+  unsigned isTile = first;
+  int isC = 0;
+  unsigned isSlot = 0;
+  auto issue = [&]() {
+    T* dst = ldSmem + (size_t)isSlot * C::STAGE_ELEMS;
     if constexpr (!XT) {
-      unsigned long long base = 0, n0 = 0;
-      if (a.mode == 0) base = (t / a.tilesPerChunk) * PB + (t % a.tilesPerChunk) * (unsigned long long)TJ;
-      else n0 = t * ((unsigned long long)TJ / a.B);
-      constexpr int VPR = TJ / VEC;                 // vectors per p row
-#pragma unroll 4
-      for (int v = tid; v < PC * VPR; v += THREADS) {
-        const int pl = v / VPR, j = (v % VPR) * VEC;
-        const unsigned long long prow = (unsigned long long)(c * PC + pl) * a.B;
-        if (a.mode == 0) {
-          cpAsync16(st + pl * TJ + j, a.X + base + prow + j);
-        } else {
-          const unsigned long long n = n0 + (unsigned long long)j / a.B;
-          const bool ok = n < a.numChunks;
-          cpAsync16Zfill(st + pl * TJ + j, ok ? a.X + n * PB + prow + (unsigned long long)j % a.B : a.X, ok);
-        }
+      if (a.mode == 0) {
+        const unsigned n = isTile / tpc, bt = isTile - n * tpc;
+        const T* src = a.X + n * PB + (unsigned long long)bt * TJ + (unsigned long long)isC * PC * a.B + ldOff;
+#pragma unroll
+        for (int i = 0; i < NLD; i++) { cpAsync16(dst, src); dst += ldSmemStep; src += ldStep; }
+      } else {
+        const unsigned long long n0 = (unsigned long long)isTile * cpt;
+        const bool ok = n0 + ldChunk < a.numChunks;
+        const T* src = ok ? a.X + n0 * PB + (unsigned long long)isC * PC * a.B + ldOff : a.X;
+#pragma unroll
+        for (int i = 0; i < NLD; i++) { cpAsync16Zfill(dst, src, ok); dst += ldSmemStep; if (ok) src += ldStep; }
       }
     } else {
-      const unsigned long long n0 = t * (unsigned long long)TJ;
-      constexpr int VPR = PC / VEC;                 // vectors per j row
-#pragma unroll 4
-      for (int v = tid; v < TJ * VPR; v += THREADS) {
-        const int j = v / VPR, pv = (v % VPR) * VEC;
-        const unsigned long long n = n0 + j;
-        const bool ok = n < a.numChunks;
-        cpAsync16Zfill(st + j * (PC + C::PAD) + pv, ok ? a.X + n * P + c * PC + pv : a.X, ok);
+      const unsigned long long n0 = (unsigned long long)isTile * TJ;
+      const T* src = a.X + n0 * P + isC * PC + ldOff;
+#pragma unroll
+      for (int i = 0; i < NLD; i++) {
+        const bool ok = n0 + ldRow + i * RPP < a.numChunks;
+        cpAsync16Zfill(dst, ok ? src : a.X, ok);
+        dst += ldSmemStep; src += ldStep;
       }
     }
+    if (++isC == C::NCH) { isC = 0; isTile += step; }
+    if (++isSlot == STAGES) isSlot = 0;
   };
 
   T acc[MQ][MJ];
@@ -139,23 +157,29 @@ gemmPassKernel(const GemmArgs<T> a) {
 
 #pragma unroll
   for (int s = 0; s < STAGES - 1; s++) {
-    if ((unsigned long long)s < total) issue(s);
+    if ((unsigned)s < total) issue();
     cpAsyncCommit();
   }
   __syncthreads();   // factor visible
 
-  for (unsigned long long s = 0; s < total; s++) {
+  unsigned curTile = first;
+  int c = 0;
+  unsigned slot = 0;
+  for (unsigned s = 0; s < total; s++) {
     cpAsyncWait<STAGES - 2>();
+#ifndef FKB_X_NOSYNC
     __syncthreads();
-    if (s + STAGES - 1 < total) issue(s + STAGES - 1);
+#endif
+#ifndef FKB_X_NOLOAD
+    if (s + STAGES - 1 < total) issue();
+#endif
     cpAsyncCommit();
 
-    const int c = (int)(s % C::NCH);
-    const T* st = stages + (size_t)(s % STAGES) * C::STAGE_ELEMS;
+    const T* st = stages + (size_t)slot * C::STAGE_ELEMS;
     const T* fr = Fs + (size_t)c * PC * Q + tq * VEC;
     if constexpr (!XT) {
       const T* xr = st + tj * VEC;
-#pragma unroll 8
+#pragma unroll UNR
       for (int pl = 0; pl < PC; pl++) {
         V xv[NGJ], fv[NGQ];
 #pragma unroll
@@ -170,7 +194,7 @@ gemmPassKernel(const GemmArgs<T> a) {
       }
     } else {
       const T* xr = st + tj * (PC + C::PAD);
-#pragma unroll 2
+#pragma unroll (UNR / VEC > 0 ? UNR / VEC : 1)
       for (int p0 = 0; p0 < PC; p0 += VEC) {
         V xv[MJ];
 #pragma unroll
@@ -189,45 +213,48 @@ gemmPassKernel(const GemmArgs<T> a) {
       }
     }
 
+#ifdef FKB_X_NOSTORE
+    if (c == C::NCH - 1 && a.alpha == T(12345)) {
+#else
     if (c == C::NCH - 1) {
+#endif
       // tile finished: stream the MQ x MJ block out and clear it
-      const unsigned long long t = first + (s / C::NCH) * step;
+      const unsigned t = curTile;
       const bool epi = a.epilogue != 0;
       const bool useY = epi && a.beta != T(0) && a.Y != nullptr;
       if constexpr (!XT) {
-        unsigned long long base = 0, n0 = 0;
-        if (a.mode == 0) base = (t / a.tilesPerChunk) * QB + (t % a.tilesPerChunk) * (unsigned long long)TJ;
-        else n0 = t * ((unsigned long long)TJ / a.B);
 #pragma unroll
-        for (int qi = 0; qi < MQ; qi++) {
-          const int q = (qi / VEC) * QS + tq * VEC + (qi % VEC);
+        for (int g = 0; g < NGJ; g++) {
+          const int j = g * JS + tj * VEC;
+          unsigned long long off;
+          bool ok = true;
+          if (a.mode == 0) {
+            const unsigned n = t / tpc, bt = t - n * tpc;
+            off = n * QB + (unsigned long long)bt * TJ + j;
+          } else {
+            const unsigned long long n = (unsigned long long)t * cpt + (unsigned)(j / a.B);
+            ok = n < a.numChunks;
+            off = n * QB + j % a.B;
+          }
+          if (ok) {
 #pragma unroll
-          for (int g = 0; g < NGJ; g++) {
-            const int j = g * JS + tj * VEC;
-            unsigned long long off;
-            bool ok = true;
-            if (a.mode == 0) {
-              off = base + (unsigned long long)q * a.B + j;
-            } else {
-              const unsigned long long n = n0 + (unsigned long long)j / a.B;
-              ok = n < a.numChunks;
-              off = n * QB + (unsigned long long)q * a.B + (unsigned long long)j % a.B;
-            }
-            if (ok) {
+            for (int qi = 0; qi < MQ; qi++) {
+              const int q = (qi / VEC) * QS + tq * VEC + (qi % VEC);
+              const unsigned long long o2 = off + (unsigned long long)q * a.B;
               V o;
 #pragma unroll
               for (int e = 0; e < VEC; e++) o.v[e] = epi ? a.alpha * acc[qi][g * VEC + e] : acc[qi][g * VEC + e];
               if (useY) {
-                const V y = *reinterpret_cast<const V*>(a.Y + off);
+                const V y = *reinterpret_cast<const V*>(a.Y + o2);
 #pragma unroll
                 for (int e = 0; e < VEC; e++) o.v[e] = fma(a.beta, y.v[e], o.v[e]);
               }
-              *reinterpret_cast<V*>(a.Z + off) = o;
+              *reinterpret_cast<V*>(a.Z + o2) = o;
             }
           }
         }
       } else {
-        const unsigned long long n0 = t * (unsigned long long)TJ;
+        const unsigned long long n0 = (unsigned long long)t * TJ;
 #pragma unroll
         for (int ji = 0; ji < MJ; ji++) {
           const unsigned long long n = n0 + tj + ji * JT;
@@ -252,7 +279,10 @@ gemmPassKernel(const GemmArgs<T> a) {
       for (int i = 0; i < MQ; i++)
 #pragma unroll
         for (int j = 0; j < MJ; j++) acc[i][j] = T(0);
+      curTile += step;
     }
+    if (++c == C::NCH) c = 0;
+    if (++slot == STAGES) slot = 0;
   }
   cpAsyncWait<0>();
 }

@@ -12,6 +12,13 @@ extern template fastKronError launchTileTW<float, true>(const Pass&, const Launc
 extern template fastKronError launchTileTW<double, false>(const Pass&, const LaunchCtx&);
 extern template fastKronError launchTileTW<double, true>(const Pass&, const LaunchCtx&);
 
+template <typename T, int TR>
+fastKronError launchTileTr(const Pass& ps, const LaunchCtx& cx);
+extern template fastKronError launchTileTr<float, 1>(const Pass&, const LaunchCtx&);
+extern template fastKronError launchTileTr<float, 2>(const Pass&, const LaunchCtx&);
+extern template fastKronError launchTileTr<double, 1>(const Pass&, const LaunchCtx&);
+extern template fastKronError launchTileTr<double, 2>(const Pass&, const LaunchCtx&);
+
 bool tileSupported(DType dt, uint32_t P, int nf, int tileB) {
   (void)dt;
   return tileInTable(P, nf, tileB > 1);
@@ -22,9 +29,18 @@ fastKronError launchTile(const Pass& ps, const LaunchCtx& cx) {
   // trailing stride, equal square factors and 16-byte aligned operands.
   const size_t es = dtypeSize(cx.dt);
   const bool wide = ps.B > 1;
-  if (ps.xsB != 1 || ps.zsB != 1) return fastKronKernelNotFound;
   for (int k = 0; k < ps.nf; k++)
     if (ps.P[k] != ps.P[0] || ps.Q[k] != ps.P[0]) return fastKronKernelNotFound;
+  if (ps.variant == 1 || ps.variant == 2) {
+    // transposing first pass: only the row-major side needs 16-byte alignment
+    if (wide) return fastKronKernelNotFound;
+    const void* rowSide = ps.variant == 1 ? cx.src : cx.dst;
+    if (((uintptr_t)rowSide & 15) || (ps.variant == 2 && ((uintptr_t)cx.Y & 15))) return fastKronKernelNotFound;
+    if (cx.dt == DType::F32)
+      return ps.variant == 1 ? launchTileTr<float, 1>(ps, cx) : launchTileTr<float, 2>(ps, cx);
+    return ps.variant == 1 ? launchTileTr<double, 1>(ps, cx) : launchTileTr<double, 2>(ps, cx);
+  }
+  if (ps.xsB != 1 || ps.zsB != 1) return fastKronKernelNotFound;
   const uint64_t W = 128 / es;
   if (wide && ps.B % W != 0) return fastKronKernelNotFound;
   if (((uintptr_t)cx.src | (uintptr_t)cx.dst | (uintptr_t)cx.Y) & 15) return fastKronKernelNotFound;

@@ -69,6 +69,11 @@ __device__ __forceinline__ void cpAsync16(void* smemDst, const void* gmemSrc) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smemDst);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmemSrc) : "memory");
 }
+__device__ __forceinline__ void cpAsync16Zfill(void* smemDst, const void* gmemSrc, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smemDst);
+  const int n = valid ? 16 : 0;     // src-size 0: nothing is read, the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmemSrc), "r"(n) : "memory");
+}
 __device__ __forceinline__ void cpAsyncWaitAll() {
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
 }
@@ -337,5 +342,123 @@ __global__ void __launch_bounds__(kTileThreads) tilePassKernel(const TileArgs<T>
     __syncthreads();
   }
 }
+
+// ---- transposing variant ---------------------------------------------------------
+// First pass of a problem whose input and output disagree on which index is
+// contiguous (KMM with opX = T: row-major in, m-contiguous out; MKM with opX = T:
+// the reverse).  The group is the trailing one (B == 1).  A super-tile is
+// [aT chunks][mT rows][G]; the row-major side moves whole [G] runs with 128-bit
+// accesses, the m-contiguous side moves mT consecutive m per access: a thread takes
+// one 16-byte piece of a fibre from shared memory and issues VEC scalar global
+// accesses, each of which is contiguous across the lanes of the warp.
+template <typename T>
+struct TileTrArgs {
+  const T* X; T* Z; const T* Y;
+  const T* F[kMaxGroup];
+  long long fsP, fsQ;
+  unsigned long long M, A;           // rows and leading chunks per row
+  int mT, aT;                        // rows / chunks per super-tile (mT a power of two)
+  unsigned long long mBlocks, numSuper;
+  T alpha, beta;
+  int epilogue;
+};
+
+constexpr unsigned long long kNoBase = ~0ull;
+
+// TR == 1: row-major input, m-contiguous output.  TR == 2: the reverse.
+template <typename T, int P, int NF, int TR>
+__global__ void __launch_bounds__(kTileThreads) tileTransposeKernel(const TileTrArgs<T> a) {
+  constexpr int THREADS = kTileThreads;
+  constexpr int VEC = Vec16<T>::N;
+  constexpr int G = ipow(P, NF);
+  using V = Vec16<T>;
+
+  extern __shared__ __align__(1024) unsigned char smemRaw[];
+  const int R = a.mT * a.aT;
+  T* tile = reinterpret_cast<T*>(smemRaw);
+  T* Fs = tile + (size_t)R * G;
+  unsigned long long* baseRow = reinterpret_cast<unsigned long long*>(Fs + NF * P * P);
+  unsigned long long* baseCol = baseRow + kTileMaxR;
+
+  for (int i = threadIdx.x; i < NF * P * P; i += THREADS) {
+    const int k = i / (P * P), p = (i / P) % P, q = i % P;
+    Fs[i] = a.F[k][(long long)p * a.fsP + (long long)q * a.fsQ];
+  }
+
+  for (unsigned long long sup = blockIdx.x; sup < a.numSuper; sup += gridDim.x) {
+    const unsigned long long m0 = (sup % a.mBlocks) * a.mT, a0 = (sup / a.mBlocks) * a.aT;
+    if ((int)threadIdx.x < R) {
+      const unsigned long long m = m0 + threadIdx.x % a.mT, ac = a0 + threadIdx.x / a.mT;
+      const bool ok = m < a.M && ac < a.A;
+      baseRow[threadIdx.x] = ok ? (m * a.A + ac) * (unsigned long long)G : kNoBase;
+      baseCol[threadIdx.x] = ac * (unsigned long long)G * a.M + m;
+    }
+    __syncthreads();
+
+    const int E = R * G;
+    const int nvec = E / VEC;
+    if (TR == 1) {
+      for (int v = threadIdx.x; v < nvec; v += THREADS) {
+        const unsigned idx = (unsigned)v * VEC;
+        const unsigned r = idx / G, w = idx % G;
+        const bool ok = baseRow[r] != kNoBase;
+        cpAsync16Zfill(tile + physIdx<T>(idx), ok ? a.X + baseRow[r] + w : a.X, ok);
+      }
+      cpAsyncWaitAll();
+    } else {
+      for (int v = threadIdx.x; v < nvec; v += THREADS) {
+        const unsigned mi = (unsigned)v % a.mT, rest = (unsigned)v / a.mT;
+        const unsigned gv = rest % (G / VEC), r = (rest / (G / VEC)) * a.mT + mi;
+        V x;
+        const bool ok = baseRow[r] != kNoBase;
+#pragma unroll
+        for (int e = 0; e < VEC; e++)
+          x.v[e] = ok ? a.X[baseCol[r] + (unsigned long long)(gv * VEC + e) * a.M] : T(0);
+        *reinterpret_cast<V*>(tile + physIdx<T>(r * G + gv * VEC)) = x;
+      }
+    }
+    __syncthreads();
+
+    StepChain<T, P, NF, 1, THREADS, NF - 1>::run(tile, Fs, E);
+
+    const bool useY = a.epilogue && a.beta != T(0) && a.Y != nullptr;
+    if (TR == 1) {
+      for (int v = threadIdx.x; v < nvec; v += THREADS) {
+        const unsigned mi = (unsigned)v % a.mT, rest = (unsigned)v / a.mT;
+        const unsigned gv = rest % (G / VEC), r = (rest / (G / VEC)) * a.mT + mi;
+        if (baseRow[r] == kNoBase) continue;
+        const V o = *reinterpret_cast<const V*>(tile + physIdx<T>(r * G + gv * VEC));
+#pragma unroll
+        for (int e = 0; e < VEC; e++) {
+          const unsigned long long off = baseCol[r] + (unsigned long long)(gv * VEC + e) * a.M;
+          T val = o.v[e];
+          if (a.epilogue) val = a.alpha * val;
+          if (useY) val = fma(a.beta, a.Y[off], val);
+          a.Z[off] = val;
+        }
+      }
+    } else {
+      for (int v = threadIdx.x; v < nvec; v += THREADS) {
+        const unsigned idx = (unsigned)v * VEC;
+        const unsigned r = idx / G, w = idx % G;
+        if (baseRow[r] == kNoBase) continue;
+        const unsigned long long goff = baseRow[r] + w;
+        V o = *reinterpret_cast<const V*>(tile + physIdx<T>(idx));
+        if (a.epilogue) {
+#pragma unroll
+          for (int i = 0; i < VEC; i++) o.v[i] = a.alpha * o.v[i];
+          if (useY) {
+            const V y = *reinterpret_cast<const V*>(a.Y + goff);
+#pragma unroll
+            for (int i = 0; i < VEC; i++) o.v[i] = fma(a.beta, y.v[i], o.v[i]);
+          }
+        }
+        *reinterpret_cast<V*>(a.Z + goff) = o;
+      }
+    }
+    __syncthreads();
+  }
+}
+
 
 }  // namespace fkb

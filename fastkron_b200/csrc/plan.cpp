@@ -131,6 +131,23 @@ fastKronError makePlan(const Problem& pr, const PlanOptions& opt, Plan* out) {
           ps.tileB = tc.tileB; ps.tileR = tc.tileR;
         }
       }
+      // First pass of a problem whose input and result disagree on the contiguous index
+      // (opX = T for MKM, opX = T for KMM): the transposing tile kernel moves [rows][G]
+      // tiles; keep G*es <= 4 KB so that at least 16 rows fit a 64 KB tile.
+      if (ps.kind == KernelKind::Generic && !opt.forceGeneric && inRow != outRow && B == 1 && P == Q &&
+          isPow2(P) && P >= 2 && P <= 32 && opt.align >= 16) {
+        const size_t es = dtypeSize(pr.dt);
+        int avail = opt.fusion ? same : 1;
+        if (avail > kMaxGroup) avail = kMaxGroup;
+        for (int n = avail; n >= 1; n--) {
+          if (!tileInTable(P, n, false)) continue;
+          uint64_t g = 1; for (int k = 0; k < n; k++) g *= P;
+          if (g * es <= 4096 && (g * es) % 16 == 0) {
+            nf = n; ps.kind = KernelKind::Tile; ps.variant = inRow ? 1 : 2; ps.tileB = 1;
+            break;
+          }
+        }
+      }
 
       if (ps.kind == KernelKind::Generic && !opt.forceGeneric && inRow == outRow && opt.align >= 16) {
         // large factors: register-blocked contraction, one factor per pass
@@ -147,7 +164,7 @@ fastKronError makePlan(const Problem& pr, const PlanOptions& opt, Plan* out) {
       ps.f0 = f0; ps.nf = nf; ps.M = pr.M; ps.A = A; ps.B = B;
       ps.xsM = cur.ms; ps.xsB = cur.cs; ps.xsG = (int64_t)B * cur.cs; ps.xsA = (int64_t)(Pg * B) * cur.cs;
       ps.zsM = nxt.ms; ps.zsB = nxt.cs; ps.zsG = (int64_t)B * nxt.cs; ps.zsA = (int64_t)(Qg * B) * nxt.cs;
-      if (ps.kind != KernelKind::Generic && !inRow) {
+      if (ps.kind != KernelKind::Generic && ps.variant == 0 && !inRow) {
         // folded view: [1][A][G][B*M], unit stride along the folded index
         ps.M = 1; ps.B = B * pr.M;
         ps.xsM = 0; ps.zsM = 0;
