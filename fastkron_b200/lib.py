@@ -30,7 +30,9 @@ API_SYMBOLS = [
     "smkmForwardStridedBatched", "dmkmForwardStridedBatched",
     "skmmForwardStridedBatched", "dkmmForwardStridedBatched",
     "fastKronMgInitCUDA", "fastKronMgSGEMM", "fastKronMgAllocX", "fastKronMgGatherY",
+    "sgemkmNoAlloc",
 ]
+NOALLOC_MAX_TEMP_ELEMS = 2 << 20
 
 
 class FastKronError(RuntimeError):

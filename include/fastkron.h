@@ -229,6 +229,24 @@ fastKronError dkmmForwardStridedBatched(fastKronHandle handle, fastKronBackend b
                                         double* Z, uint64_t strideZ, uint32_t batchCount,
                                         double* Intermediates[], uint64_t strideIntermediates[]);
 
+/* ---- GeMKM without caller-provided temporaries -------------------------------------
+ * This function has no counterpart in the reference.  It is sgemkm for callers that
+ * may not allocate device memory (code inside another framework's fixed memory plan,
+ * processes where allocation after start-up is forbidden): the two temporaries come
+ * from a static buffer inside the library, FASTKRON_NOALLOC_MAX_TEMP_ELEMS floats each,
+ * resident on every GPU that loads the library.  Problems whose gekmmSizes() tmpElems
+ * exceeds that are rejected with fastKronInvalidArgument.  The first call on a device
+ * looks up the buffer's address and should be made before any stream capture.  All
+ * calls on one device share the buffer: calls that can overlap on the GPU race.  The
+ * handle must have been given a stream with fastKronInitCUDA; the device that was
+ * current then must be current now. */
+#define FASTKRON_NOALLOC_MAX_TEMP_ELEMS (2u << 20)
+fastKronError sgemkmNoAlloc(fastKronHandle handle,
+                            uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
+                            const float* X, fastKronOp opX,
+                            const float* const Fs[], fastKronOp opFs,
+                            float* Z, float alpha, float beta, const float* Y);
+
 #ifdef __cplusplus
 }
 #endif
