@@ -169,6 +169,32 @@ fastKronError Engine::run(Problem pr, const CallOperands& ops) {
   return fastKronSuccess;
 }
 
+// One kernel launch: the pass's own kernel family, the generic kernel when that family
+// declines a single-factor pass, optional event bracketing for the benchmark.
+fastKronError Engine::launchPass(const Pass& ps, const LaunchCtx& cx) {
+  cudaStream_t stream = cx.stream;
+  cudaEvent_t evEnd = nullptr;
+  if (profiling_) {
+    while (evPool_.size() < evUsed_ + 2) {
+      cudaEvent_t ev;
+      if (cudaEventCreate(&ev) != cudaSuccess) return fastKronOtherError;
+      evPool_.push_back(ev);
+    }
+    cudaEventRecord(evPool_[evUsed_], stream);
+    evEnd = evPool_[evUsed_ + 1];
+    evUsed_ += 2;
+  }
+  int ranKind = (int)ps.kind;
+  fastKronError e = fastKronKernelNotFound;
+  if (ps.kind == KernelKind::Tile) e = launchTile(ps, cx);
+  else if (ps.kind == KernelKind::Gemm) e = launchGemm(ps, cx);
+  if (e == fastKronKernelNotFound && ps.nf == 1) { e = launchGeneric(ps, cx); ranKind = (int)KernelKind::Generic; }
+  if (evEnd) { cudaEventRecord(evEnd, stream); evKinds_.push_back(ranKind); }
+  if (e != fastKronSuccess) return e;
+  gLaunches++;
+  return fastKronSuccess;
+}
+
 fastKronError Engine::execute(const Problem& pr, const Plan& plan, const CallOperands& ops,
                               cudaStream_t stream, int smCount) {
   auto resolve = [&](Buf b) -> void* {
@@ -194,25 +220,8 @@ fastKronError Engine::execute(const Problem& pr, const Plan& plan, const CallOpe
     for (int k = 0; k < ps.nf; k++) cx.F[k] = ops.Fs[ps.f0 + k];
     factorStrides(pr.mm, pr.opF, ps.P[0], ps.Q[0], &cx.fsP, &cx.fsQ);
 
-    cudaEvent_t evEnd = nullptr;
-    if (profiling_) {
-      while (evPool_.size() < evUsed_ + 2) {
-        cudaEvent_t ev;
-        if (cudaEventCreate(&ev) != cudaSuccess) return fastKronOtherError;
-        evPool_.push_back(ev);
-      }
-      cudaEventRecord(evPool_[evUsed_], stream);
-      evEnd = evPool_[evUsed_ + 1];
-      evUsed_ += 2;
-    }
-    int ranKind = (int)ps.kind;
-    fastKronError e = fastKronKernelNotFound;
-    if (ps.kind == KernelKind::Tile) e = launchTile(ps, cx);
-    else if (ps.kind == KernelKind::Gemm) e = launchGemm(ps, cx);
-    if (e == fastKronKernelNotFound && ps.nf == 1) { e = launchGeneric(ps, cx); ranKind = (int)KernelKind::Generic; }
-    if (evEnd) { cudaEventRecord(evEnd, stream); evKinds_.push_back(ranKind); }
+    fastKronError e = launchPass(ps, cx);
     if (e != fastKronSuccess) return e;
-    gLaunches++;
   }
   return fastKronSuccess;
 }

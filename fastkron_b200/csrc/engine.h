@@ -61,6 +61,9 @@ class Engine {
   fastKronError execute(const Problem& pr, const Plan& plan, const CallOperands& ops,
                         cudaStream_t stream, int smCount);
 
+  // Launch one pass (with fallback to the generic kernel and optional event timing).
+  fastKronError launchPass(const Pass& ps, const LaunchCtx& cx);
+
   MgState* mg = nullptr;
 
   // Optional per-pass timing: when enabled, execute() brackets every kernel launch

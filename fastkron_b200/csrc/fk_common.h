@@ -93,6 +93,7 @@ struct PlanOptions {
   bool fusion = true;           // fastKronOptionsUseFusion
   bool haveT2 = true;           // caller supplied temp2
   bool forceGeneric = false;    // debugging / parity cross-check
+  bool isolateFirst = false;    // factor 0 gets a pass of its own (multi-GPU: that pass redistributes)
   size_t smemBudget = 200 * 1024;
   // pointer alignment of X / Z / temps in bytes (vector kernels need 16)
   int  align = 16;

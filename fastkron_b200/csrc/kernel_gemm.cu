@@ -20,6 +20,7 @@ static fastKronError launchGemmOne(const Pass& ps, const LaunchCtx& cx, int mode
   else if (mode == 1) { const unsigned long long per = TJ / ps.B; a.numTiles = (a.numChunks + per - 1) / per; }
   else { a.numTiles = (a.numChunks + TJ - 1) / TJ; }
   a.alpha = (T)cx.alpha; a.beta = (T)cx.beta; a.epilogue = ps.epilogue ? 1 : 0;
+  a.sc = cx.scatter;
   if (a.numTiles == 0) return fastKronSuccess;
   if (a.numTiles >= (1ull << 31) / C::NCH) return fastKronKernelNotFound;   // 32-bit tile counters
 

@@ -35,7 +35,20 @@ struct GemmArgs {
   int mode;                          // 0: B >= TJ, 1: 4 <= B < TJ, 2: B == 1 (XT)
   T alpha, beta;
   int epilogue;
+  Scatter sc;                        // parts > 0: rows go to other GPUs' buffers
 };
+
+// Pointer to output row (chunk n, row q), trailing position 0.
+template <typename T, int Q>
+__device__ __forceinline__ T* gemmOutRow(const GemmArgs<T>& a, unsigned long long n, int q) {
+  if (a.sc.parts > 0) {
+    const unsigned d = (unsigned)q / (unsigned)a.sc.qPer, ql = (unsigned)q - d * (unsigned)a.sc.qPer;
+    const unsigned long long m = n / a.sc.aLoc, ac = n - m * a.sc.aLoc;
+    return reinterpret_cast<T*>(a.sc.base[d]) + (long long)m * a.sc.sM + (long long)ac * a.sc.sA +
+           (long long)ql * a.sc.sQ + a.sc.zOff;
+  }
+  return a.Z + n * ((unsigned long long)Q * a.B) + (unsigned long long)q * a.B;
+}
 
 __device__ __forceinline__ void cpAsyncCommit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
@@ -226,30 +239,30 @@ gemmPassKernel(const GemmArgs<T> a) {
 #pragma unroll
         for (int g = 0; g < NGJ; g++) {
           const int j = g * JS + tj * VEC;
-          unsigned long long off;
+          unsigned long long n, col;
           bool ok = true;
           if (a.mode == 0) {
-            const unsigned n = t / tpc, bt = t - n * tpc;
-            off = n * QB + (unsigned long long)bt * TJ + j;
+            const unsigned nn = t / tpc, bt = t - nn * tpc;
+            n = nn; col = (unsigned long long)bt * TJ + j;
           } else {
-            const unsigned long long n = (unsigned long long)t * cpt + (unsigned)(j / a.B);
+            n = (unsigned long long)t * cpt + (unsigned)(j / a.B);
             ok = n < a.numChunks;
-            off = n * QB + j % a.B;
+            col = j % a.B;
           }
           if (ok) {
 #pragma unroll
             for (int qi = 0; qi < MQ; qi++) {
               const int q = (qi / VEC) * QS + tq * VEC + (qi % VEC);
-              const unsigned long long o2 = off + (unsigned long long)q * a.B;
+              T* dst = gemmOutRow<T, Q>(a, n, q) + col;
               V o;
 #pragma unroll
               for (int e = 0; e < VEC; e++) o.v[e] = epi ? a.alpha * acc[qi][g * VEC + e] : acc[qi][g * VEC + e];
               if (useY) {
-                const V y = *reinterpret_cast<const V*>(a.Y + o2);
+                const V y = *reinterpret_cast<const V*>(a.Y + (dst - a.Z));
 #pragma unroll
                 for (int e = 0; e < VEC; e++) o.v[e] = fma(a.beta, y.v[e], o.v[e]);
               }
-              *reinterpret_cast<V*>(a.Z + o2) = o;
+              *reinterpret_cast<V*>(dst) = o;
             }
           }
         }
@@ -261,6 +274,13 @@ gemmPassKernel(const GemmArgs<T> a) {
           if (n < a.numChunks) {
 #pragma unroll
             for (int g = 0; g < NGQ; g++) {
+              if (a.sc.parts > 0) {
+                // redistributed rows are not contiguous in q: one element at a time
+#pragma unroll
+                for (int e = 0; e < VEC; e++)
+                  *gemmOutRow<T, Q>(a, n, g * QS + tq * VEC + e) = epi ? a.alpha * acc[g * VEC + e][ji] : acc[g * VEC + e][ji];
+                continue;
+              }
               const unsigned long long off = n * Q + g * QS + tq * VEC;
               V o;
 #pragma unroll

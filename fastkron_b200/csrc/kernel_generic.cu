@@ -20,6 +20,8 @@ struct GenericDims {
   long long xs[4];
   long long zs[4];
   int qDim;                 // which of the four is q
+  int dimId[4];             // 0 = m, 1 = a, 2 = q, 3 = b for each enumerated index
+  unsigned long long chunkA; // extent of the a index (chunk n = m*chunkA + a)
 };
 
 template <typename T>
@@ -32,6 +34,7 @@ struct GenericArgs {
   T alpha, beta;
   int epilogue;
   unsigned long long total;
+  Scatter sc;
 };
 
 template <typename T>
@@ -42,6 +45,7 @@ __global__ void __launch_bounds__(256) genericPassKernel(const GenericArgs<T> a)
     unsigned long long rem = idx;
     long long xoff = 0, zoff = 0;
     unsigned long long q = 0;
+    unsigned long long coord[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int k = 0; k < 4; k++) {
       const unsigned long long c = rem % a.d.size[k];
@@ -49,6 +53,7 @@ __global__ void __launch_bounds__(256) genericPassKernel(const GenericArgs<T> a)
       xoff += (long long)c * a.d.xs[k];
       zoff += (long long)c * a.d.zs[k];
       if (k == a.d.qDim) q = c;
+      coord[a.d.dimId[k]] = c;
     }
     const T* xp = a.X + xoff;
     const T* fp = a.F + (long long)q * a.fsQ;
@@ -59,7 +64,16 @@ __global__ void __launch_bounds__(256) genericPassKernel(const GenericArgs<T> a)
       acc = a.alpha * acc;
       if (a.beta != T(0) && a.Y != nullptr) acc = fma(a.beta, a.Y[zoff], acc);
     }
-    a.Z[zoff] = acc;
+    if (a.sc.parts > 0) {
+      // chunk index n = m*A + a of the pass; split it the way the scatter wants it
+      T* base = (T*)a.sc.base[q / a.sc.qPer];
+      const unsigned long long n = coord[0] * a.d.chunkA + coord[1];
+      const long long off = (long long)(n / a.sc.aLoc) * a.sc.sM + (long long)(n % a.sc.aLoc) * a.sc.sA +
+                            (long long)(q % a.sc.qPer) * a.sc.sQ + a.sc.zOff + (long long)coord[3];
+      base[off] = acc;
+    } else {
+      a.Z[zoff] = acc;
+    }
   }
 }
 
@@ -73,9 +87,11 @@ static fastKronError launchGenericT(const Pass& ps, const LaunchCtx& cx) {
 
   // enumerate the output indices in order of ascending output stride so that
   // neighbouring threads write neighbouring addresses
-  struct D { unsigned long long n; long long xs, zs; int isQ; };
-  D ds[4] = { {ps.M, ps.xsM, ps.zsM, 0}, {ps.A, ps.xsA, ps.zsA, 0},
-              {ps.Q[0], 0, ps.zsG, 1},   {ps.B, ps.xsB, ps.zsB, 0} };
+  struct D { unsigned long long n; long long xs, zs; int isQ; int id; };
+  D ds[4] = { {ps.M, ps.xsM, ps.zsM, 0, 0}, {ps.A, ps.xsA, ps.zsA, 0, 1},
+              {ps.Q[0], 0, ps.zsG, 1, 2},   {ps.B, ps.xsB, ps.zsB, 0, 3} };
+  a.sc = cx.scatter;
+  a.d.chunkA = ps.A;
   for (int i = 0; i < 4; i++)
     for (int j = i + 1; j < 4; j++) {
       auto key = [](const D& d) { return d.n == 1 ? (long long)(1ll << 62) : (d.zs < 0 ? -d.zs : d.zs); };
@@ -86,6 +102,7 @@ static fastKronError launchGenericT(const Pass& ps, const LaunchCtx& cx) {
   for (int i = 0; i < 4; i++) {
     a.d.size[i] = ds[i].n; a.d.xs[i] = ds[i].xs; a.d.zs[i] = ds[i].zs;
     if (ds[i].isQ) a.d.qDim = i;
+    a.d.dimId[i] = ds[i].id;
     a.total *= ds[i].n;
   }
   if (a.total == 0) return fastKronSuccess;

@@ -7,6 +7,19 @@
 
 namespace fkb {
 
+// Output redirection of a pass whose result is redistributed over several GPUs (the
+// all-to-all of the column-sharded multi-GPU path, fused into the producing kernel's
+// stores).  With chunk n = m*aLoc + a, output row (n, q) and trailing position b:
+//   address = base[q / qPer] + m*sM + a*sA + (q % qPer)*sQ + zOff + b
+// base[d] is a buffer on GPU d, reached with plain peer stores.  parts == 0: off.
+constexpr int kMaxParts = 8;
+struct Scatter {
+  int parts = 0;
+  void* base[kMaxParts] = {nullptr};
+  unsigned long long qPer = 1, aLoc = 1;
+  long long sM = 0, sA = 0, sQ = 0, zOff = 0;
+};
+
 // Everything a kernel launcher needs besides the Pass itself.
 struct LaunchCtx {
   cudaStream_t stream = nullptr;
@@ -18,6 +31,7 @@ struct LaunchCtx {
   int64_t fsP = 1, fsQ = 1;       // factor element (p,q) at p*fsP + q*fsQ
   double alpha = 1.0, beta = 0.0; // applied only when pass.epilogue
   int smCount = 148;
+  Scatter scatter;                // only honoured by the Generic and Gemm launchers
 };
 
 // Each returns fastKronKernelNotFound when the pass does not fit the kernel

@@ -112,7 +112,8 @@ fastKronError makePlan(const Problem& pr, const PlanOptions& opt, Plan* out) {
     } else {
       // how many factors could share a pass with factor i
       int same = 1;
-      while (i - same >= 0 && pr.P[i - same] == P && pr.Q[i - same] == Q) same++;
+      while (i - same >= 0 && pr.P[i - same] == P && pr.Q[i - same] == Q &&
+             !(opt.isolateFirst && i - same == 0)) same++;
 
       uint64_t outColsOne = curCols / P * Q;
       Layout nxtOne = matLayout(pr, outColsOne);

@@ -23,9 +23,10 @@ extern "C" {
 #endif
 
 /* `streams` points to an array of `gpus` cudaStream_t, stream g on device g.
- * gpusInM * gpusInK must equal gpus; -1 selects gpusInM = 1, gpusInK = gpus.
- * gpuLocalKrons is the largest number of factors applied between two
- * exchanges; -1 lets the library choose.
+ * gpusInM * gpusInK must equal gpus (otherwise fastKronInvalidArgument); the
+ * defaults are the reference's: gpusInM = -1 selects 1, gpusInK = -1 selects 2.
+ * gpuLocalKrons (factors applied between two exchanges in the reference) is
+ * accepted and ignored: the schedule here always uses two exchanges.
  * (reference: include/fastkronMg.h:10, src/kernel_db/cuda_kernel_db.cu:62-186) */
 fastKronError fastKronMgInitCUDA(fastKronHandle handle, void* streams, int gpus,
                                  int gpusInM FASTKRON_MG_DEFAULT(-1),
