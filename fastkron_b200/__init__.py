@@ -12,7 +12,7 @@ from typing import List, Optional
 from . import lib as _lib
 from .lib import FastKronError  # noqa: F401
 
-__all__ = ["FastKron", "gemkm", "gekmm", "gekmm_sizes", "FastKronError"]
+__all__ = ["FastKron", "gemkm", "gekmm", "gemkm_host", "gekmm_sizes", "FastKronError"]
 
 
 def _torch():
@@ -237,3 +237,100 @@ def gekmm(fs: List, x, alpha: float = 1.0, beta: float = 0.0, y: Optional[object
     """Z = alpha * (F1 (x) ... (x) FN) X + beta * Y with F_i of shape (Q_i, P_i) and X of
     shape (prod P_i, M)."""
     return _run("kmm", x, fs, alpha, beta, y)
+
+
+class HostGeMKM:
+    """GeMKM on HOST operands: X and Z live in pinned host memory, the product runs on the GPU.
+
+    Rows of a GeMKM are independent, so the call is cut into row slabs and pipelined on three
+    streams: slab i+1 travels host->device while slab i is multiplied and slab i-1 travels
+    device->host (PCIe is full duplex, so the two copy directions overlap as well).  Device
+    memory holds two input slabs, two output slabs and one pair of temporaries, whatever the
+    size of X.  The factors stay on the device.  Construct once per shape, call many times."""
+
+    def __init__(self, M, ps, qs, dtype=None, rows_per_slab=None, device_budget_bytes=8 << 30):
+        torch = _torch()
+        self.torch = torch
+        self.dtype = dtype or torch.float32
+        self.es = 4 if self.dtype == torch.float32 else 8
+        self.M, self.ps, self.qs = int(M), [int(p) for p in ps], [int(q) for q in qs]
+        self.K = 1
+        for p in self.ps:
+            self.K *= p
+        self.L = 1
+        for q in self.qs:
+            self.L *= q
+        self.h = FastKron()
+        if rows_per_slab is None:
+            _, te1 = self.h.sizes(1, self.ps, self.qs)
+            per_row = (2 * self.K + 2 * self.L + 2 * te1) * self.es
+            rows_per_slab = max(1, min(self.M, device_budget_bytes // per_row))
+            # at least 8 slabs when possible, so that the un-overlapped first copy-in and
+            # last copy-out are a small part of the call
+            rows_per_slab = max(1, min(rows_per_slab, -(-self.M // 8)))
+        self.rows = int(rows_per_slab)
+        _, te = self.h.sizes(self.rows, self.ps, self.qs)
+        dev = "cuda"
+        self.xd = [torch.empty(self.rows * self.K, dtype=self.dtype, device=dev) for _ in range(2)]
+        self.zd = [torch.empty(self.rows * self.L, dtype=self.dtype, device=dev) for _ in range(2)]
+        self.t1 = torch.empty(te, dtype=self.dtype, device=dev)
+        self.t2 = torch.empty(te, dtype=self.dtype, device=dev)
+        self.s_in, self.s_mm, self.s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        self.h.set_stream(self.s_mm)
+
+    def __call__(self, x_host, fs, z_host, alpha=1.0, beta=0.0, y_host=None):
+        """x_host [M, K] and z_host [M, L]: pinned, contiguous host tensors; fs: device factors.
+        Returns after z_host is complete.  beta*Y is not supported on this path."""
+        torch = self.torch
+        if beta != 0.0 or y_host is not None:
+            raise ValueError("HostGeMKM computes alpha * X (F1 (x) ... (x) FN) only")
+        dch = "s" if self.dtype == torch.float32 else "d"
+        cur = torch.cuda.current_stream()
+        for s in (self.s_in, self.s_mm, self.s_out):
+            s.wait_stream(cur)
+        xh, zh = x_host.view(self.M, self.K), z_host.view(self.M, self.L)
+        nslab = -(-self.M // self.rows)
+        in_done = [None, None]      # event: slab copied into xd[b]
+        mm_done = [None, None]      # event: product of buffer b finished (xd[b] free, zd[b] full)
+        out_done = [None, None]     # event: zd[b] copied out
+        fptr = [f.data_ptr() for f in fs]
+        for i in range(nslab):
+            b = i & 1
+            r0 = i * self.rows
+            r = min(self.rows, self.M - r0)
+            with torch.cuda.stream(self.s_in):
+                if mm_done[b] is not None:
+                    self.s_in.wait_event(mm_done[b])
+                self.xd[b][: r * self.K].view(r, self.K).copy_(xh[r0:r0 + r], non_blocking=True)
+                in_done[b] = self.s_in.record_event()
+            with torch.cuda.stream(self.s_mm):
+                self.s_mm.wait_event(in_done[b])
+                if out_done[b] is not None:
+                    self.s_mm.wait_event(out_done[b])
+                self.h.raw_gemm("mkm", dch, r, self.ps, self.qs, self.xd[b].data_ptr(), _lib.OP_N, fptr, _lib.OP_N,
+                                self.zd[b].data_ptr(), float(alpha), 0.0, 0, self.t1.data_ptr(), self.t2.data_ptr())
+                mm_done[b] = self.s_mm.record_event()
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(mm_done[b])
+                zh[r0:r0 + r].copy_(self.zd[b][: r * self.L].view(r, self.L), non_blocking=True)
+                out_done[b] = self.s_out.record_event()
+        cur.wait_stream(self.s_out)
+        cur.wait_stream(self.s_mm)
+        return z_host
+
+    def close(self):
+        self.h.close()
+
+
+def gemkm_host(x_host, fs, z_host, alpha=1.0):
+    """One-shot form of HostGeMKM (allocates its device slabs on every call)."""
+    M = x_host.shape[0]
+    ps = [f.shape[0] for f in fs]
+    qs = [f.shape[1] for f in fs]
+    op = HostGeMKM(M, ps, qs, dtype=x_host.dtype)
+    try:
+        op(x_host, fs, z_host, alpha)
+        _torch().cuda.synchronize()
+    finally:
+        op.close()
+    return z_host

@@ -56,7 +56,7 @@ fastKronError launchGemm(const Pass& ps, const LaunchCtx& cx) {
     const int mode = xt ? 2 : (ps.B % TJ == 0 ? 0 : 1);
     if (P == 64 && Q == 64) {
       if (xt) return launchGemmOne<float, 64, 64, TJ, 32, 3, 8, 8, true, 8, 3>(ps, cx, mode);
-      return launchGemmOne<float, 64, 64, TJ, 32, 3, 8, 8, false, 8, 3>(ps, cx, mode);
+      return launchGemmOne<float, 64, 64, TJ, 32, 3, 8, 8, false, 16, 3>(ps, cx, mode);
     }
     if (P == 128 && Q == 128) {
       if (xt) return launchGemmOne<float, 128, 128, TJ, 32, 2, 8, 8, true, 8, 1>(ps, cx, mode);

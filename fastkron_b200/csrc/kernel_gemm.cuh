@@ -180,12 +180,8 @@ gemmPassKernel(const GemmArgs<T> a) {
   unsigned slot = 0;
   for (unsigned s = 0; s < total; s++) {
     cpAsyncWait<STAGES - 2>();
-#ifndef FKB_X_NOSYNC
     __syncthreads();
-#endif
-#ifndef FKB_X_NOLOAD
     if (s + STAGES - 1 < total) issue();
-#endif
     cpAsyncCommit();
 
     const T* st = stages + (size_t)slot * C::STAGE_ELEMS;
@@ -226,16 +222,45 @@ gemmPassKernel(const GemmArgs<T> a) {
       }
     }
 
-#ifdef FKB_X_NOSTORE
-    if (c == C::NCH - 1 && a.alpha == T(12345)) {
-#else
     if (c == C::NCH - 1) {
-#endif
       // tile finished: stream the MQ x MJ block out and clear it
       const unsigned t = curTile;
       const bool epi = a.epilogue != 0;
       const bool useY = epi && a.beta != T(0) && a.Y != nullptr;
-      if constexpr (!XT) {
+      // Common case first and kept short (the steady-state loop has to stay small enough
+      // for the instruction cache): plain pass, no epilogue, no redistribution.
+      if (!epi && a.sc.parts == 0 && (XT || a.mode == 0)) {
+        if constexpr (!XT) {
+          const unsigned nn = t / tpc, bt = t - nn * tpc;
+          T* p0 = a.Z + nn * QB + (unsigned long long)bt * TJ + tj * VEC + (unsigned long long)(tq * VEC) * a.B;
+#pragma unroll
+          for (int qi = 0; qi < MQ; qi++) {
+            T* pq = p0 + (unsigned long long)((qi / VEC) * QS + (qi % VEC)) * a.B;
+#pragma unroll
+            for (int g = 0; g < NGJ; g++) {
+              V o;
+#pragma unroll
+              for (int e = 0; e < VEC; e++) o.v[e] = acc[qi][g * VEC + e];
+              *reinterpret_cast<V*>(pq + g * JS) = o;
+            }
+          }
+        } else {
+          const unsigned long long n0 = (unsigned long long)t * TJ + tj;
+          T* p0 = a.Z + n0 * Q + tq * VEC;
+#pragma unroll
+          for (int ji = 0; ji < MJ; ji++) {
+            if (n0 + ji * JT < a.numChunks) {
+#pragma unroll
+              for (int g = 0; g < NGQ; g++) {
+                V o;
+#pragma unroll
+                for (int e = 0; e < VEC; e++) o.v[e] = acc[g * VEC + e][ji];
+                *reinterpret_cast<V*>(p0 + (size_t)ji * JT * Q + g * QS) = o;
+              }
+            }
+          }
+        }
+      } else if constexpr (!XT) {
 #pragma unroll
         for (int g = 0; g < NGJ; g++) {
           const int j = g * JS + tj * VEC;
