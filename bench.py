@@ -45,7 +45,10 @@ CONFIGS = {
 # reduced copies for quick functional runs of this script (--config C5s etc.)
 CONFIGS["C5s"] = dict(CONFIGS["C5"], M=16, ps=[64] * 3, qs=[64] * 3)
 CONFIGS["C1s"] = dict(CONFIGS["C1"], M=64)
-CONFIGS["C5m"] = dict(CONFIGS["C5"], M=256, ps=[64] * 3, qs=[64] * 3)      # 268 MB operand: profiling size
+# profiling sizes: operands larger than L2, a few hundred MB each
+CONFIGS["C5m"] = dict(CONFIGS["C5"], M=256, ps=[64] * 3, qs=[64] * 3)
+CONFIGS["C2p"] = dict(CONFIGS["C2"], M=4)
+CONFIGS["C4p"] = dict(CONFIGS["C4"], M=256)
 
 
 def flops_library(c, M=None):

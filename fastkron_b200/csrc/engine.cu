@@ -141,7 +141,7 @@ fastKronError Engine::run(Problem pr, const CallOperands& ops) {
   }
   const Plan& plan = it->second;
 
-  if (pr.batch == 1) return execute(pr, plan, ops, stream_, smCount_);
+  if (pr.batch == 1) return execute(pr, plan, ops, stream_, smCount());
 
   // Strided batch: the same plan once per entry, on offset operands.
   std::vector<const void*> fs(pr.N);
@@ -163,7 +163,7 @@ fastKronError Engine::run(Problem pr, const CallOperands& ops) {
       }
       o.intermediates = inter.data();
     }
-    fastKronError e = execute(pr, plan, o, stream_, smCount_);
+    fastKronError e = execute(pr, plan, o, stream_, smCount());
     if (e != fastKronSuccess) return e;
   }
   return fastKronSuccess;

@@ -48,7 +48,12 @@ class Engine {
   fastKronError setStream(void* ptrToStream);
   bool cudaReady() const { return cudaReady_; }
   cudaStream_t stream() const { return stream_; }
-  int smCount() const { return smCount_; }
+  // SMs a launch may plan for: the device's count scaled by the handle's share (see
+  // setSmShare); persistent kernels size their grids from it.
+  int smCount() const { int n = (int)(smCount_ * smShare_ + 0.5f); return n < 1 ? 1 : n; }
+  // Let two handles that work concurrently on different streams each take a part of the
+  // GPU: share in (0, 1].
+  void setSmShare(float s) { smShare_ = (s > 0.f && s <= 1.f) ? s : 1.f; }
 
   // Result / temporary element counts (per batch entry).
   fastKronError sizes(const Problem& pr, size_t* yElems, size_t* tmpElems) const;
@@ -83,6 +88,7 @@ class Engine {
   cudaStream_t stream_ = nullptr;
   int device_ = 0;
   int smCount_ = 148;
+  float smShare_ = 1.f;
   std::map<std::string, Plan> planCache_;
 };
 

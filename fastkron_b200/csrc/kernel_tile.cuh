@@ -46,6 +46,10 @@ struct TileArgs {
 };
 
 constexpr int kTileThreads = 128;
+#ifndef FKB_STEP_UNROLL
+#define FKB_STEP_UNROLL 4
+#endif
+constexpr int kStepUnroll = FKB_STEP_UNROLL;   // p iterations unrolled in a contraction step
 constexpr int kTileMaxR = 64;
 
 __host__ __device__ constexpr int ipow(int b, int e) { return e == 0 ? 1 : b * ipow(b, e - 1); }
@@ -64,6 +68,21 @@ struct alignas(16) Vec16 {
   static constexpr int N = 16 / sizeof(T);
   T v[N];
 };
+
+// W consecutive elements, W * sizeof(T) <= 16 bytes, naturally aligned.
+template <typename T, int W>
+struct alignas(W * sizeof(T)) VecW {
+  T v[W];
+};
+
+// Accumulator budget of one thread in a contraction step: 64 registers' worth of
+// outputs (64 floats / 32 doubles), i.e. kAcc/P whole fibres.
+template <typename T>
+struct StepShape {
+  static constexpr int kAcc = 256 / (int)sizeof(T);
+};
+template <typename T, int P>
+__host__ __device__ constexpr int stepFibres() { return StepShape<T>::kAcc / P > 0 ? StepShape<T>::kAcc / P : 1; }
 
 __device__ __forceinline__ void cpAsync16(void* smemDst, const void* gmemSrc) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smemDst);
@@ -88,15 +107,19 @@ __host__ __device__ __forceinline__ void schedFence() {
 
 // ---- one contraction step over a tile of E elements, mode stride S ----------
 
-// Strided fibres, S >= VEC: a thread owns VEC neighbouring fibres per group and
-// U groups at a time; every access is one 128-bit shared-memory transaction.
+// Strided fibres, S >= W: a thread owns NFIB = kAcc/P fibres, as U groups of W
+// neighbouring ones (W * sizeof(T) <= 16 bytes); every access is one W-wide
+// shared-memory transaction, consecutive lanes take consecutive groups.
 template <typename T, int P, int S, int THREADS>
 __host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const T* __restrict__ Fs, int E, int tid) {
   constexpr int VEC = Vec16<T>::N;
-  constexpr int U = (16 / P) > 1 ? (16 / P) : 1;
+  constexpr int NFIB = stepFibres<T, P>();
+  constexpr int W = NFIB < VEC ? NFIB : VEC;
+  constexpr int U = NFIB / W;
   constexpr int FV = P < VEC ? P : VEC;
-  using V = Vec16<T>;
-  const int nvg = E / (P * VEC);
+  using V = VecW<T, W>;
+  using FVv = Vec16<T>;
+  const int nvg = E / (P * W);
   for (int vg0 = tid; vg0 < nvg; vg0 += THREADS * U) {
     unsigned pb[U];
     bool ok[U];
@@ -105,19 +128,21 @@ __host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const
       int vg = vg0 + u * THREADS;
       ok[u] = vg < nvg;
       if (!ok[u]) vg = vg0;
-      const unsigned lo = (unsigned)vg % (S / VEC);
-      const unsigned hi = (unsigned)vg / (S / VEC);
-      pb[u] = physIdx<T>(hi * (unsigned)(S * P) + lo * VEC);
+      const unsigned lo = (unsigned)vg % (S / W);
+      const unsigned hi = (unsigned)vg / (S / W);
+      pb[u] = physIdx<T>(hi * (unsigned)(S * P) + lo * W);
     }
-    T acc[U][VEC][P];
+    T acc[U][W][P];
 #pragma unroll
     for (int u = 0; u < U; u++)
 #pragma unroll
-      for (int k = 0; k < VEC; k++)
+      for (int k = 0; k < W; k++)
 #pragma unroll
         for (int q = 0; q < P; q++) acc[u][k][q] = T(0);
 
-#pragma unroll
+    // Partially unrolled on purpose: a fully unrolled step of P = 16 or 32 is several
+    // thousand instructions and the fused kernels then miss in the instruction cache.
+#pragma unroll(P < kStepUnroll ? P : kStepUnroll)
     for (int p = 0; p < P; p++) {
       V xv[U];
 #pragma unroll
@@ -127,7 +152,7 @@ __host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const
       for (int q0 = 0; q0 < P; q0 += FV) {
         T f[FV];
         if (FV == VEC) {
-          const V fv = *reinterpret_cast<const V*>(Fs + p * P + q0);
+          const FVv fv = *reinterpret_cast<const FVv*>(Fs + p * P + q0);
 #pragma unroll
           for (int i = 0; i < FV; i++) f[i] = fv.v[i];
         } else {
@@ -137,7 +162,7 @@ __host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const
 #pragma unroll
         for (int u = 0; u < U; u++)
 #pragma unroll
-          for (int k = 0; k < VEC; k++)
+          for (int k = 0; k < W; k++)
 #pragma unroll
             for (int i = 0; i < FV; i++) acc[u][k][q0 + i] = fma(xv[u].v[k], f[i], acc[u][k][q0 + i]);
       }
@@ -149,7 +174,7 @@ __host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const
       for (int u = 0; u < U; u++) {
         V ov;
 #pragma unroll
-        for (int k = 0; k < VEC; k++) ov.v[k] = acc[u][k][q];
+        for (int k = 0; k < W; k++) ov.v[k] = acc[u][k][q];
         if (ok[u]) *reinterpret_cast<V*>(tile + (pb[u] ^ physIdx<T>((unsigned)(q * S)))) = ov;
       }
     }
@@ -161,8 +186,7 @@ __host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const
 template <typename T, int P, int THREADS>
 __host__ __device__ __forceinline__ void stepContig(T* __restrict__ tile, const T* __restrict__ Fs, int E, int tid) {
   constexpr int VEC = Vec16<T>::N;
-  constexpr int U = (16 / P) > 1 ? (16 / P) : 1;
-  constexpr int NFIB = U * VEC;
+  constexpr int NFIB = stepFibres<T, P>();
   using V = Vec16<T>;
   const int nfib = E / P;
   for (int f0 = tid; f0 < nfib; f0 += THREADS * NFIB) {
@@ -181,7 +205,7 @@ __host__ __device__ __forceinline__ void stepContig(T* __restrict__ tile, const 
 #pragma unroll
       for (int q = 0; q < P; q++) acc[k][q] = T(0);
 
-#pragma unroll
+#pragma unroll((P / VEC) < (kStepUnroll / VEC) ? (P / VEC) : (kStepUnroll / VEC > 0 ? kStepUnroll / VEC : 1))
     for (int p0 = 0; p0 < P; p0 += VEC) {
       V xv[NFIB];
 #pragma unroll
@@ -241,7 +265,9 @@ __host__ __device__ __forceinline__ void stepScalar(T* __restrict__ tile, const 
 template <typename T, int P, int S, int THREADS>
 __host__ __device__ __forceinline__ void stepDispatch(T* tile, const T* Fs, int E, int tid) {
   constexpr int VEC = Vec16<T>::N;
-  if constexpr (S >= VEC) {
+  constexpr int NFIB = stepFibres<T, P>();
+  constexpr int W = NFIB < VEC ? NFIB : VEC;
+  if constexpr (S >= W && S % W == 0) {
     stepStrided<T, P, S, THREADS>(tile, Fs, E, tid);
   } else if constexpr (S == 1 && P >= VEC) {
     stepContig<T, P, THREADS>(tile, Fs, E, tid);
@@ -280,7 +306,7 @@ __host__ __device__ __forceinline__ unsigned long long tileGlobalOffset(const un
 }
 
 template <typename T, int P, int NF, bool WIDE>
-__global__ void __launch_bounds__(kTileThreads) tilePassKernel(const TileArgs<T> a) {
+__global__ void __launch_bounds__(kTileThreads, 4) tilePassKernel(const TileArgs<T> a) {
   constexpr int THREADS = kTileThreads;
   constexpr int VEC = Vec16<T>::N;
   constexpr int BT = WIDE ? (int)(128 / sizeof(T)) : 1;
@@ -367,7 +393,7 @@ constexpr unsigned long long kNoBase = ~0ull;
 
 // TR == 1: row-major input, m-contiguous output.  TR == 2: the reverse.
 template <typename T, int P, int NF, int TR>
-__global__ void __launch_bounds__(kTileThreads) tileTransposeKernel(const TileTrArgs<T> a) {
+__global__ void __launch_bounds__(kTileThreads, 4) tileTransposeKernel(const TileTrArgs<T> a) {
   constexpr int THREADS = kTileThreads;
   constexpr int VEC = Vec16<T>::N;
   constexpr int G = ipow(P, NF);

@@ -105,8 +105,9 @@ static void mgScatter2(const MgRank& r, Scatter* sc) {
 }
 
 // Phase 1: modes N..2 of the local block; the last pass redistributes into recvPeers[d].
+// stage: 0 = all passes, 1 = only the local passes, 2 = only the redistributing pass.
 static fastKronError mgPhase1(Engine* e, const MgRank& r, const float* x, const float* const* Fs, float* t1,
-                              float* t2, void* const recvPeers[]) {
+                              float* t2, void* const recvPeers[], int stage = 0) {
   fastKronError err = mgCheck(r);
   if (err != fastKronSuccess) return err;
   const uint32_t p1loc = r.Ps[0] / r.gk;
@@ -124,6 +125,7 @@ static fastKronError mgPhase1(Engine* e, const MgRank& r, const float* x, const 
   for (size_t k = 0; k < plan.passes.size(); k++) {
     Pass ps = plan.passes[k];
     const bool last = (k + 1 == plan.passes.size());
+    if ((stage == 1 && last) || (stage == 2 && !last)) continue;
     LaunchCtx cx;
     cx.stream = r.stream; cx.dt = DType::F32; cx.smCount = r.smCount;
     auto buf = [&](Buf b) -> void* {
@@ -391,6 +393,20 @@ fastKronError fkbMgRankPhase1(fastKronHandle handle, int rank, int world, uint32
   MgRank r;
   r.g = rank; r.gk = world; r.M = M; r.N = N; r.Ps = Ps; r.Qs = Qs; r.stream = e->stream(); r.smCount = e->smCount();
   return mgPhase1(e, r, x, Fs, temp1, temp2, peerRecv);
+}
+
+// The same phase in two calls, so that a host can put an event between the local passes
+// (stage 1) and the redistributing pass (stage 2).
+fastKronError fkbMgRankPhase1Stage(fastKronHandle handle, int rank, int world, uint32_t M, uint32_t N,
+                                   uint32_t Ps[], uint32_t Qs[], const float* x, const float* const Fs[],
+                                   float* temp1, float* temp2, void* const peerRecv[], int stage) {
+  if (!handle || !Ps || !Qs || !x || !Fs || !temp1 || !temp2 || !peerRecv || stage < 1 || stage > 2)
+    return fastKronInvalidArgument;
+  Engine* e = E(handle);
+  if (!e->cudaReady()) return fastKronBackendNotAvailable;
+  MgRank r;
+  r.g = rank; r.gk = world; r.M = M; r.N = N; r.Ps = Ps; r.Qs = Qs; r.stream = e->stream(); r.smCount = e->smCount();
+  return mgPhase1(e, r, x, Fs, temp1, temp2, peerRecv, stage);
 }
 
 fastKronError fkbMgRankPhase2(fastKronHandle handle, int rank, int world, uint32_t M, uint32_t N,

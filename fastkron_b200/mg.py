@@ -160,6 +160,103 @@ class RankGeMKM:
         self.h.close()
 
 
+class PipelinedRankGeMKM:
+    """The same product with the rows cut into `parts` independent slices, each a RankGeMKM
+    of its own on its own stream, and each handle sized for 1/parts of the SMs.
+
+    Why: in a column-sharded step two of the four passes stream their output to the peers
+    and are bound by NVLink, the other two are bound by arithmetic.  Rows are independent,
+    so while one slice is in an NVLink-bound pass another slice can use the idle FP32 pipes.
+    The slices start one after the other; the GPU's scheduler interleaves their kernels."""
+
+    def __init__(self, M, ps, qs, parts=2, group=None):
+        import torch
+        self.torch = torch
+        self.parts = parts if M % parts == 0 else 1
+        self.M, self.Mp = int(M), int(M) // self.parts
+        self.streams = [torch.cuda.Stream() for _ in range(self.parts)]
+        self.slices = []
+        import torch.distributed as dist
+        for i, s in enumerate(self.streams):
+            # a communicator of its own per slice: barriers of different slices must not
+            # queue behind one another on a shared collective stream
+            g = group
+            if dist.is_initialized() and dist.get_world_size(group) > 1 and i > 0:
+                g = dist.new_group(ranks=list(range(dist.get_world_size())))
+            with torch.cuda.stream(s):
+                r = RankGeMKM(self.Mp, ps, qs, group=g)
+                r.h.set_stream(s)
+                r.lib.fkbSetSmShare(r.h.h, ctypes.c_float(1.0 / self.parts))
+                self.slices.append(r)
+        self.world, self.rank = self.slices[0].world, self.slices[0].rank
+        self.Lloc = self.slices[0].Lloc
+        torch.cuda.synchronize()
+
+    def run(self, x, fs, join=True):
+        """x: this rank's [M, K/G] block.  Returns the list of per-slice result blocks
+        ([M/parts, L/G] each, in row order).
+
+        Slice i+1 starts its local passes when slice i has finished its own, so that one
+        slice's arithmetic-bound passes run beside the other's NVLink-bound ones.  With
+        join=True the caller's stream waits for all slices before and after; join=False
+        leaves the slices free-running from one call to the next (call `join()` before
+        reading the results) so that the stagger carries over between consecutive calls."""
+        torch = self.torch
+        cur = torch.cuda.current_stream()
+        xs = x.view(self.M, -1)
+        outs = []
+        if join:
+            for s in self.streams:
+                s.wait_stream(cur)
+        if self.world == 1:
+            for i, (r, s) in enumerate(zip(self.slices, self.streams)):
+                with torch.cuda.stream(s):
+                    outs.append(r.run(xs[i * self.Mp:(i + 1) * self.Mp], fs))
+            if join:
+                self.join()
+            return outs
+        n = len(self.slices[0].ps)
+        L = self.slices[0].lib
+        F = _lib.ptrarr([f.data_ptr() for f in fs])
+        # every rank issues the same sequence of kernels and barriers, slice after slice
+        prev_local_done = None
+        for i, (r, s) in enumerate(zip(self.slices, self.streams)):
+            with torch.cuda.stream(s):
+                P, Q = _lib.u32arr(r.ps), _lib.u32arr(r.qs)
+                xi = xs[i * self.Mp:(i + 1) * self.Mp]
+                args = (r.h.h, ctypes.c_int(r.rank), ctypes.c_int(r.world), ctypes.c_uint32(r.M),
+                        ctypes.c_uint32(n), P, Q, ctypes.c_void_p(xi.data_ptr()), F,
+                        ctypes.c_void_p(r.t1.data_ptr()), ctypes.c_void_p(r.t2.data_ptr()),
+                        _lib.ptrarr(r.peer_recv))
+                if prev_local_done is not None:
+                    s.wait_event(prev_local_done)
+                _lib.check(L.fkbMgRankPhase1Stage(*args, ctypes.c_int(1)))
+                prev_local_done = s.record_event()
+                _lib.check(L.fkbMgRankPhase1Stage(*args, ctypes.c_int(2)))
+                r.barrier()
+        for i, (r, s) in enumerate(zip(self.slices, self.streams)):
+            with torch.cuda.stream(s):
+                P, Q = _lib.u32arr(r.ps), _lib.u32arr(r.qs)
+                _lib.check(L.fkbMgRankPhase2(r.h.h, ctypes.c_int(r.rank), ctypes.c_int(r.world),
+                                             ctypes.c_uint32(r.M), ctypes.c_uint32(n), P, Q,
+                                             ctypes.c_void_p(r.recv_ptr), ctypes.c_void_p(fs[0].data_ptr()),
+                                             _lib.ptrarr(r.peer_result)))
+                r.barrier()
+                outs.append(r.result.view(r.M, r.Lloc))
+        if join:
+            self.join()
+        return outs
+
+    def join(self):
+        cur = self.torch.cuda.current_stream()
+        for s in self.streams:
+            cur.wait_stream(s)
+
+    def close(self):
+        for r in self.slices:
+            r.close()
+
+
 def scatter_desc(phase, rank, world, ps, qs):
     """The redistribution map of a phase as a dict (host arithmetic only; no GPU needed):
     destination of output row (m, a, q), trailing position b is rank q // qPer at offset
