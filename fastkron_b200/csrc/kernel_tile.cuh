@@ -45,7 +45,14 @@ struct TileArgs {
   int epilogue;
 };
 
-constexpr int kTileThreads = 128;
+#ifndef FKB_TILE_THREADS
+#define FKB_TILE_THREADS 128
+#endif
+#ifndef FKB_TILE_MINB
+#define FKB_TILE_MINB 4
+#endif
+constexpr int kTileThreads = FKB_TILE_THREADS;
+constexpr int kTileMinBlocks = FKB_TILE_MINB;
 #ifndef FKB_STEP_UNROLL
 #define FKB_STEP_UNROLL 4
 #endif
@@ -305,8 +312,36 @@ __host__ __device__ __forceinline__ unsigned long long tileGlobalOffset(const un
   }
 }
 
+// Visit every 16-byte vector of a super-tile of nsub sub-tiles once: f(tileIndex, globalOffset).
+// A thread keeps its position inside the sub-tile and walks sub-tiles, so the per-vector
+// address work is an add (narrow: the super-tile is one contiguous run).
+template <typename T, bool WIDE, int SUB, int BT, int THREADS, typename F>
+__device__ __forceinline__ void forEachTileVector(const unsigned long long* bases, unsigned long long contigBase,
+                                                  int nsub, unsigned long long B, F&& f) {
+  constexpr int VEC = Vec16<T>::N;
+  constexpr int VPS = SUB / VEC;                     // vectors per sub-tile
+  if constexpr (!WIDE) {
+    const int nvec = nsub * VPS;
+    for (int v = threadIdx.x; v < nvec; v += THREADS) f((unsigned)v * VEC, contigBase + (unsigned long long)v * VEC);
+  } else if constexpr (VPS >= THREADS) {
+    for (int r = 0; r < nsub; r++) {
+      const unsigned long long base = bases[r];
+#pragma unroll 4
+      for (int j = threadIdx.x; j < VPS; j += THREADS) {
+        const unsigned w = (unsigned)j * VEC;
+        f((unsigned)r * SUB + w, base + (unsigned long long)(w / BT) * B + (w % BT));
+      }
+    }
+  } else {
+    constexpr int SPT = THREADS / VPS;                // sub-tiles per sweep of the CTA
+    const unsigned w = (threadIdx.x % VPS) * VEC;
+    const unsigned long long gw = (unsigned long long)(w / BT) * B + (w % BT);
+    for (int r = threadIdx.x / VPS; r < nsub; r += SPT) f((unsigned)r * SUB + w, bases[r] + gw);
+  }
+}
+
 template <typename T, int P, int NF, bool WIDE>
-__global__ void __launch_bounds__(kTileThreads, 4) tilePassKernel(const TileArgs<T> a) {
+__global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tilePassKernel(const TileArgs<T> a) {
   constexpr int THREADS = kTileThreads;
   constexpr int VEC = Vec16<T>::N;
   constexpr int BT = WIDE ? (int)(128 / sizeof(T)) : 1;
@@ -339,32 +374,29 @@ __global__ void __launch_bounds__(kTileThreads, 4) tilePassKernel(const TileArgs
     __syncthreads();
 
     const int E = nsub * SUB;
-    const int nvec = E / VEC;
-    for (int v = threadIdx.x; v < nvec; v += THREADS) {
-      const unsigned idx = (unsigned)v * VEC;
-      const unsigned long long goff = tileGlobalOffset<WIDE, SUB, BT>(bases, st0 * G, idx, a.B);
+    forEachTileVector<T, WIDE, SUB, BT, THREADS>(bases, st0 * G, nsub, a.B, [&](unsigned idx, unsigned long long goff) {
       cpAsync16(tile + physIdx<T>(idx), a.X + goff);
-    }
+    });
     cpAsyncWaitAll();
     __syncthreads();
 
     StepChain<T, P, NF, BT, THREADS, NF - 1>::run(tile, Fs, E);
 
-    for (int v = threadIdx.x; v < nvec; v += THREADS) {
-      const unsigned idx = (unsigned)v * VEC;
-      const unsigned long long goff = tileGlobalOffset<WIDE, SUB, BT>(bases, st0 * G, idx, a.B);
+    const bool epi = a.epilogue != 0;
+    const bool useY = epi && a.beta != T(0) && a.Y != nullptr;
+    forEachTileVector<T, WIDE, SUB, BT, THREADS>(bases, st0 * G, nsub, a.B, [&](unsigned idx, unsigned long long goff) {
       V o = *reinterpret_cast<const V*>(tile + physIdx<T>(idx));
-      if (a.epilogue) {
+      if (epi) {
 #pragma unroll
         for (int i = 0; i < VEC; i++) o.v[i] = a.alpha * o.v[i];
-        if (a.beta != T(0) && a.Y != nullptr) {
+        if (useY) {
           const V y = *reinterpret_cast<const V*>(a.Y + goff);
 #pragma unroll
           for (int i = 0; i < VEC; i++) o.v[i] = fma(a.beta, y.v[i], o.v[i]);
         }
       }
       *reinterpret_cast<V*>(a.Z + goff) = o;
-    }
+    });
     __syncthreads();
   }
 }
@@ -393,7 +425,7 @@ constexpr unsigned long long kNoBase = ~0ull;
 
 // TR == 1: row-major input, m-contiguous output.  TR == 2: the reverse.
 template <typename T, int P, int NF, int TR>
-__global__ void __launch_bounds__(kTileThreads, 4) tileTransposeKernel(const TileTrArgs<T> a) {
+__global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tileTransposeKernel(const TileTrArgs<T> a) {
   constexpr int THREADS = kTileThreads;
   constexpr int VEC = Vec16<T>::N;
   constexpr int G = ipow(P, NF);
