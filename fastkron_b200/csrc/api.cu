@@ -278,6 +278,14 @@ int fkbSetSmShare(fastKronHandle handle, float share) {
   return 0;
 }
 
+// Upper bound on the tiles one CTA of the large-factor kernel processes (0 = persistent
+// CTAs).  A bound makes CTAs retire often, which lets small kernels of other streams in.
+int fkbSetTilesPerCta(fastKronHandle handle, int n) {
+  if (!handle) return (int)fastKronInvalidArgument;
+  E(handle)->setTilesPerCta(n);
+  return 0;
+}
+
 // ---- introspection used by the host-side tests (not part of the reference ABI) --
 // Writes the textual plan of a problem into buf; returns the number of passes
 // or a negative fastKronError.

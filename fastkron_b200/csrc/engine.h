@@ -54,6 +54,9 @@ class Engine {
   // Let two handles that work concurrently on different streams each take a part of the
   // GPU: share in (0, 1].
   void setSmShare(float s) { smShare_ = (s > 0.f && s <= 1.f) ? s : 1.f; }
+  // See LaunchCtx::tilesPerCta.
+  void setTilesPerCta(int n) { tilesPerCta_ = n > 0 ? n : 0; }
+  int tilesPerCta() const { return tilesPerCta_; }
 
   // Result / temporary element counts (per batch entry).
   fastKronError sizes(const Problem& pr, size_t* yElems, size_t* tmpElems) const;
@@ -89,6 +92,7 @@ class Engine {
   int device_ = 0;
   int smCount_ = 148;
   float smShare_ = 1.f;
+  int tilesPerCta_ = 0;
   std::map<std::string, Plan> planCache_;
 };
 

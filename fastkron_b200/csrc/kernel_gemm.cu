@@ -21,6 +21,8 @@ static fastKronError launchGemmOne(const Pass& ps, const LaunchCtx& cx, int mode
   else { a.numTiles = (a.numChunks + TJ - 1) / TJ; }
   a.alpha = (T)cx.alpha; a.beta = (T)cx.beta; a.epilogue = ps.epilogue ? 1 : 0;
   a.sc = cx.scatter;
+  a.pSplit = cx.pSplit; a.pOuter = cx.pOuter; a.nStride = cx.nStride;
+  if (a.pSplit != 0 && mode != 0) return fastKronKernelNotFound;
   if (a.numTiles == 0) return fastKronSuccess;
   if (a.numTiles >= (1ull << 31) / C::NCH) return fastKronKernelNotFound;   // 32-bit tile counters
 
@@ -35,6 +37,10 @@ static fastKronError launchGemmOne(const Pass& ps, const LaunchCtx& cx, int mode
     ctasPerSm = n;
   }
   unsigned long long grid = (unsigned long long)cx.smCount * ctasPerSm;
+  if (cx.tilesPerCta > 0) {
+    const unsigned long long want = (a.numTiles + cx.tilesPerCta - 1) / cx.tilesPerCta;
+    if (want > grid) grid = want;
+  }
   if (grid > a.numTiles) grid = a.numTiles;
   kern<<<(unsigned)grid, C::THREADS, C::SMEM, cx.stream>>>(a);
   return cudaToFk(cudaGetLastError());

@@ -36,6 +36,11 @@ struct GemmArgs {
   T alpha, beta;
   int epilogue;
   Scatter sc;                        // parts > 0: rows go to other GPUs' buffers
+  // Split contraction index on the input side (mode 0 only): row p of chunk n lives at
+  // n*nStride + (p / pSplit)*pOuter + (p % pSplit)*B.  pSplit == 0: plain [n][P][B].
+  // (Input of the multi-GPU phase 2, received as [sender][M][P/G][B].)
+  unsigned pSplit = 0;
+  unsigned long long pOuter = 0, nStride = 0;
 };
 
 // Pointer to output row (chunk n, row q), trailing position 0.
@@ -138,9 +143,20 @@ gemmPassKernel(const GemmArgs<T> a) {
     if constexpr (!XT) {
       if (a.mode == 0) {
         const unsigned n = isTile / tpc, bt = isTile - n * tpc;
-        const T* src = a.X + n * PB + (unsigned long long)bt * TJ + (unsigned long long)isC * PC * a.B + ldOff;
+        if (a.pSplit == 0) {
+          const T* src = a.X + n * PB + (unsigned long long)bt * TJ + (unsigned long long)isC * PC * a.B + ldOff;
 #pragma unroll
-        for (int i = 0; i < NLD; i++) { cpAsync16(dst, src); dst += ldSmemStep; src += ldStep; }
+          for (int i = 0; i < NLD; i++) { cpAsync16(dst, src); dst += ldSmemStep; src += ldStep; }
+        } else {
+          const T* base = a.X + n * a.nStride + (unsigned long long)bt * TJ + ldCol;
+#pragma unroll
+          for (int i = 0; i < NLD; i++) {
+            const unsigned p = (unsigned)(isC * PC + ldRow + i * RPP);
+            const unsigned po = p / a.pSplit, pi = p - po * a.pSplit;
+            cpAsync16(dst, base + po * a.pOuter + (unsigned long long)pi * a.B);
+            dst += ldSmemStep;
+          }
+        }
       } else {
         const unsigned long long n0 = (unsigned long long)isTile * cpt;
         const bool ok = n0 + ldChunk < a.numChunks;
@@ -275,10 +291,26 @@ gemmPassKernel(const GemmArgs<T> a) {
             col = j % a.B;
           }
           if (ok) {
+            // everything of the output address that does not depend on q, once per group
+            const bool sc = a.sc.parts > 0;
+            unsigned long long rowBase;
+            if (sc) {
+              const unsigned long long m = n / a.sc.aLoc, ac = n - m * a.sc.aLoc;
+              rowBase = (unsigned long long)((long long)m * a.sc.sM + (long long)ac * a.sc.sA + a.sc.zOff) + col;
+            } else {
+              rowBase = n * QB + col;
+            }
+            const unsigned qPer = (unsigned)a.sc.qPer;
 #pragma unroll
             for (int qi = 0; qi < MQ; qi++) {
               const int q = (qi / VEC) * QS + tq * VEC + (qi % VEC);
-              T* dst = gemmOutRow<T, Q>(a, n, q) + col;
+              T* dst;
+              if (sc) {
+                const unsigned d = (unsigned)q / qPer, ql = (unsigned)q - d * qPer;
+                dst = reinterpret_cast<T*>(a.sc.base[d]) + rowBase + (unsigned long long)ql * (unsigned long long)a.sc.sQ;
+              } else {
+                dst = a.Z + rowBase + (unsigned long long)q * a.B;
+              }
               V o;
 #pragma unroll
               for (int e = 0; e < VEC; e++) o.v[e] = epi ? a.alpha * acc[qi][g * VEC + e] : acc[qi][g * VEC + e];

@@ -32,6 +32,13 @@ struct LaunchCtx {
   double alpha = 1.0, beta = 0.0; // applied only when pass.epilogue
   int smCount = 148;
   Scatter scatter;                // only honoured by the Generic and Gemm launchers
+  // Gemm launcher only: input rows split as [outer][chunk][pSplit][B] (see GemmArgs)
+  unsigned pSplit = 0;
+  unsigned long long pOuter = 0, nStride = 0;
+  // Gemm launcher: 0 = persistent CTAs (one per slot, looping over all tiles); n > 0 = at most
+  // n tiles per CTA, so that CTAs retire every few tens of microseconds and a small kernel
+  // from another stream (a collective used as a barrier) can get onto the GPU in between.
+  int tilesPerCta = 0;
 };
 
 // Each returns fastKronKernelNotFound when the pass does not fit the kernel

@@ -106,8 +106,9 @@ static void mgScatter2(const MgRank& r, Scatter* sc) {
 
 // Phase 1: modes N..2 of the local block; the last pass redistributes into recvPeers[d].
 // stage: 0 = all passes, 1 = only the local passes, 2 = only the redistributing pass.
+// packed: destination blocks hold only this rank's rows, [M][P1/G][Q2/G][B] (staged form).
 static fastKronError mgPhase1(Engine* e, const MgRank& r, const float* x, const float* const* Fs, float* t1,
-                              float* t2, void* const recvPeers[], int stage = 0) {
+                              float* t2, void* const recvPeers[], int stage = 0, bool packed = false) {
   fastKronError err = mgCheck(r);
   if (err != fastKronSuccess) return err;
   const uint32_t p1loc = r.Ps[0] / r.gk;
@@ -127,7 +128,7 @@ static fastKronError mgPhase1(Engine* e, const MgRank& r, const float* x, const 
     const bool last = (k + 1 == plan.passes.size());
     if ((stage == 1 && last) || (stage == 2 && !last)) continue;
     LaunchCtx cx;
-    cx.stream = r.stream; cx.dt = DType::F32; cx.smCount = r.smCount;
+    cx.stream = r.stream; cx.dt = DType::F32; cx.smCount = r.smCount; cx.tilesPerCta = e->tilesPerCta();
     auto buf = [&](Buf b) -> void* {
       switch (b) { case Buf::X: return const_cast<float*>(x); case Buf::T1: return t1; case Buf::T2: return t2;
                    default: return recvPeers[r.g]; }
@@ -141,6 +142,10 @@ static fastKronError mgPhase1(Engine* e, const MgRank& r, const float* x, const 
       if (ps.nf != 1 || ps.f0 != 0) return fastKronOtherError;
       if (ps.kind == KernelKind::Tile) ps.kind = KernelKind::Generic;   // only Generic/Gemm redistribute
       mgScatter1(r, &cx.scatter);
+      if (packed) {
+        cx.scatter.sM = (long long)(cx.scatter.aLoc * cx.scatter.qPer) * cx.scatter.sQ;   // P1/G rows per m
+        cx.scatter.zOff = 0;
+      }
       for (int d = 0; d < r.gk; d++) cx.scatter.base[d] = recvPeers[d];
     }
     err = e->launchPass(ps, cx);
@@ -162,7 +167,7 @@ static fastKronError mgPhase2(Engine* e, const MgRank& r, const float* recv, con
   ps.zsM = (int64_t)(r.Qs[0] * B2); ps.zsA = ps.zsM; ps.zsG = (int64_t)B2; ps.zsB = 1;
   ps.kind = gemmEligible(DType::F32, r.Ps[0], r.Qs[0], B2) ? KernelKind::Gemm : KernelKind::Generic;
   LaunchCtx cx;
-  cx.stream = r.stream; cx.dt = DType::F32; cx.smCount = r.smCount;
+  cx.stream = r.stream; cx.dt = DType::F32; cx.smCount = r.smCount; cx.tilesPerCta = e->tilesPerCta();
   cx.src = recv; cx.dst = resultPeers[r.g];
   cx.F[0] = F0;
   factorStrides(MMType::MKM, fastKronOp_N, ps.P[0], ps.Q[0], &cx.fsP, &cx.fsQ);
@@ -418,6 +423,81 @@ fastKronError fkbMgRankPhase2(fastKronHandle handle, int rank, int world, uint32
   MgRank r;
   r.g = rank; r.gk = world; r.M = M; r.N = N; r.Ps = Ps; r.Qs = Qs; r.stream = e->stream(); r.smCount = e->smCount();
   return mgPhase2(e, r, recv, F0, peerResult);
+}
+
+// ---- staged form: the kernels write per-destination blocks into LOCAL staging buffers and
+// the host moves the blocks with copy engines (cudaMemcpyAsync / cudaMemcpy2DAsync to
+// IPC-mapped peer buffers), so NVLink traffic needs no SM and overlaps other rows' passes.
+// Large-factor (64/128) shapes only: the phase-2 kernel reads its input as received,
+// [sender][M][P1/G][B2].
+//   stage1: G blocks of M*(P1/G)*(Q2/G)*B elements, block d = [M][P1/G][Q2/G][B] for rank d
+//   recv  : G blocks of the same size, block s = what rank s staged for this rank
+//   stage2: G blocks of M*(Q1/G)*B2 elements, block d = [M][Q1/G][B2] for rank d, to be placed
+//           at columns [g*B2, (g+1)*B2) of rank d's [M*(Q1/G)][Q2*B] result.
+fastKronError fkbMgRankPhase1Staged(fastKronHandle handle, int rank, int world, uint32_t M, uint32_t N,
+                                    uint32_t Ps[], uint32_t Qs[], const float* x, const float* const Fs[],
+                                    float* temp1, float* temp2, float* stage1, int stage) {
+  if (!handle || !Ps || !Qs || !x || !Fs || !temp1 || !temp2 || !stage1 || stage < 0 || stage > 2)
+    return fastKronInvalidArgument;
+  Engine* e = E(handle);
+  if (!e->cudaReady()) return fastKronBackendNotAvailable;
+  MgRank r;
+  r.g = rank; r.gk = world; r.M = M; r.N = N; r.Ps = Ps; r.Qs = Qs; r.stream = e->stream(); r.smCount = e->smCount();
+  fastKronError err = mgCheck(r);
+  if (err != fastKronSuccess) return err;
+  const uint64_t p1loc = Ps[0] / world, q2loc = Qs[1] / world, B = prodQ(r, 2);
+  const uint64_t blk = (uint64_t)M * p1loc * q2loc * B;
+  void* bases[kMaxParts];
+  for (int d = 0; d < world; d++) bases[d] = stage1 + (size_t)d * blk;
+  // same kernels as the fused form; only the redistribution map differs (all bases local,
+  // rows of a block packed as [M][P1/G][Q2/G][B])
+  return mgPhase1(e, r, x, Fs, temp1, temp2, bases, stage, /*packed=*/true);
+}
+
+fastKronError fkbMgRankPhase2Staged(fastKronHandle handle, int rank, int world, uint32_t M, uint32_t N,
+                                    uint32_t Ps[], uint32_t Qs[], const float* recv, const float* F0,
+                                    float* stage2) {
+  if (!handle || !Ps || !Qs || !recv || !F0 || !stage2) return fastKronInvalidArgument;
+  Engine* e = E(handle);
+  if (!e->cudaReady()) return fastKronBackendNotAvailable;
+  MgRank r;
+  r.g = rank; r.gk = world; r.M = M; r.N = N; r.Ps = Ps; r.Qs = Qs; r.stream = e->stream(); r.smCount = e->smCount();
+  fastKronError err = mgCheck(r);
+  if (err != fastKronSuccess) return err;
+  const uint64_t p1loc = Ps[0] / world, q1loc = Qs[0] / world;
+  const uint64_t B2 = (Qs[1] / world) * prodQ(r, 2);
+  if (!gemmEligible(DType::F32, Ps[0], Qs[0], B2) || B2 % (uint64_t)gemmTileJ(DType::F32) != 0)
+    return fastKronKernelNotFound;
+  Pass ps;
+  ps.f0 = 0; ps.nf = 1; ps.M = M; ps.A = 1; ps.B = B2;
+  ps.P[0] = Ps[0]; ps.Q[0] = Qs[0];
+  ps.xsM = (int64_t)(Ps[0] * B2); ps.xsA = ps.xsM; ps.xsG = (int64_t)B2; ps.xsB = 1;
+  ps.zsM = (int64_t)(Qs[0] * B2); ps.zsA = ps.zsM; ps.zsG = (int64_t)B2; ps.zsB = 1;
+  ps.kind = KernelKind::Gemm;
+  LaunchCtx cx;
+  cx.stream = r.stream; cx.dt = DType::F32; cx.smCount = r.smCount; cx.tilesPerCta = e->tilesPerCta();
+  cx.src = recv; cx.dst = stage2;
+  cx.F[0] = F0;
+  factorStrides(MMType::MKM, fastKronOp_N, ps.P[0], ps.Q[0], &cx.fsP, &cx.fsQ);
+  cx.pSplit = (unsigned)p1loc; cx.pOuter = (unsigned long long)M * p1loc * B2; cx.nStride = p1loc * B2;
+  cx.scatter.parts = world; cx.scatter.qPer = q1loc; cx.scatter.aLoc = 1;
+  cx.scatter.sM = (long long)(q1loc * B2); cx.scatter.sA = 0; cx.scatter.sQ = (long long)B2; cx.scatter.zOff = 0;
+  const uint64_t blk = (uint64_t)M * q1loc * B2;
+  for (int d = 0; d < world; d++) cx.scatter.base[d] = stage2 + (size_t)d * blk;
+  // the launcher refuses the split input unless it runs the kernel: no generic fallback here
+  fastKronError le = launchGemm(ps, cx);
+  return le;
+}
+
+// Stream-ordered copies for the staged form (plain cudaMemcpyAsync / cudaMemcpy2DAsync,
+// device to device; the destination may be an IPC mapping of a peer's buffer).
+int fkbCopyAsync(void* dst, const void* src, size_t bytes, void* stream) {
+  return (int)cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+}
+int fkbCopy2DAsync(void* dst, size_t dpitch, const void* src, size_t spitch, size_t widthBytes, size_t height,
+                   void* stream) {
+  return (int)cudaMemcpy2DAsync(dst, dpitch, src, spitch, widthBytes, height, cudaMemcpyDeviceToDevice,
+                                (cudaStream_t)stream);
 }
 
 // The two redistribution maps as plain numbers, for host-side (CPU) tests of the schedule:

@@ -160,23 +160,121 @@ class RankGeMKM:
         self.h.close()
 
 
+class StagedRankGeMKM(RankGeMKM):
+    """Same product, other transport: the kernels write per-destination blocks into local
+    staging buffers and copy engines move them (cudaMemcpyAsync / cudaMemcpy2DAsync into the
+    peers' IPC-mapped buffers) on a second stream.  The NVLink traffic then costs no SM time
+    and overlaps whatever else the GPU computes.  For the large-factor shapes (64, 128) only;
+    RankGeMKM (stores fused into the kernels) covers everything else."""
+
+    def __init__(self, M, ps, qs, group=None):
+        super().__init__(M, ps, qs, group=group)
+        torch = self.torch
+        if self.world == 1:
+            return
+        G = self.world
+        B = _prod(self.qs[2:])
+        self.blk1 = self.M * (self.ps[0] // G) * (self.qs[1] // G) * B
+        self.B2 = (self.qs[1] // G) * B
+        self.blk2 = self.M * (self.qs[0] // G) * self.B2
+        self.stage1 = torch.empty(G * self.blk1, dtype=torch.float32, device="cuda")
+        self.stage2 = torch.empty(G * self.blk2, dtype=torch.float32, device="cuda")
+        # copies and barriers go first whenever they are ready; the compute kernels retire
+        # their CTAs every few tiles so that the barrier's small kernel finds a free slot
+        self.copy_stream = torch.cuda.Stream(priority=-1)
+        self.lib.fkbSetTilesPerCta(self.h.h, ctypes.c_int(int(__import__("os").environ.get("FASTKRON_MG_TILES_PER_CTA", "8"))))
+
+    def _copies1(self, s):
+        L, g, G = self.lib, self.rank, self.world
+        for k in range(G):
+            d = (g + k) % G
+            dst = self.peer_recv[d] + 4 * g * self.blk1
+            rc = L.fkbCopyAsync(ctypes.c_void_p(dst), ctypes.c_void_p(self.stage1.data_ptr() + 4 * d * self.blk1),
+                                ctypes.c_size_t(4 * self.blk1), ctypes.c_void_p(s.cuda_stream))
+            if rc != 0:
+                raise RuntimeError("peer copy failed (cuda error %d)" % rc)
+
+    def _copies2(self, s):
+        L, g, G = self.lib, self.rank, self.world
+        rows = self.M * (self.qs[0] // G)
+        dpitch = 4 * self.Lloc // (self.qs[0] // G)         # bytes of one (m, q1) row of the result
+        for k in range(G):
+            d = (g + k) % G
+            dst = self.peer_result[d] + 4 * g * self.B2
+            rc = L.fkbCopy2DAsync(ctypes.c_void_p(dst), ctypes.c_size_t(dpitch),
+                                  ctypes.c_void_p(self.stage2.data_ptr() + 4 * d * self.blk2),
+                                  ctypes.c_size_t(4 * self.B2), ctypes.c_size_t(4 * self.B2), ctypes.c_size_t(rows),
+                                  ctypes.c_void_p(s.cuda_stream))
+            if rc != 0:
+                raise RuntimeError("peer 2-D copy failed (cuda error %d)" % rc)
+
+    def run(self, x, fs, after=None):
+        """Enqueues the whole step; returns (result view, event that marks its completion).
+        `after`: optional event the local passes wait for (used to stagger row slices)."""
+        torch = self.torch
+        if self.world == 1:
+            return super().run(x, fs), None
+        n = len(self.ps)
+        L = self.lib
+        sC, sX = self.h.stream, self.copy_stream
+        P, Q = _lib.u32arr(self.ps), _lib.u32arr(self.qs)
+        F = _lib.ptrarr([f.data_ptr() for f in fs])
+        with torch.cuda.stream(sC):
+            if after is not None:
+                sC.wait_event(after)
+            _lib.check(L.fkbMgRankPhase1Staged(self.h.h, ctypes.c_int(self.rank), ctypes.c_int(self.world),
+                                               ctypes.c_uint32(self.M), ctypes.c_uint32(n), P, Q,
+                                               ctypes.c_void_p(x.data_ptr()), F, ctypes.c_void_p(self.t1.data_ptr()),
+                                               ctypes.c_void_p(self.t2.data_ptr()),
+                                               ctypes.c_void_p(self.stage1.data_ptr()), ctypes.c_int(1)))
+            self.local_done = sC.record_event()
+            _lib.check(L.fkbMgRankPhase1Staged(self.h.h, ctypes.c_int(self.rank), ctypes.c_int(self.world),
+                                               ctypes.c_uint32(self.M), ctypes.c_uint32(n), P, Q,
+                                               ctypes.c_void_p(x.data_ptr()), F, ctypes.c_void_p(self.t1.data_ptr()),
+                                               ctypes.c_void_p(self.t2.data_ptr()),
+                                               ctypes.c_void_p(self.stage1.data_ptr()), ctypes.c_int(2)))
+            e1 = sC.record_event()
+        with torch.cuda.stream(sX):
+            sX.wait_event(e1)
+            self._copies1(sX)
+            self.barrier()
+            e2 = sX.record_event()
+        with torch.cuda.stream(sC):
+            sC.wait_event(e2)
+            _lib.check(L.fkbMgRankPhase2Staged(self.h.h, ctypes.c_int(self.rank), ctypes.c_int(self.world),
+                                               ctypes.c_uint32(self.M), ctypes.c_uint32(n), P, Q,
+                                               ctypes.c_void_p(self.recv_ptr), ctypes.c_void_p(fs[0].data_ptr()),
+                                               ctypes.c_void_p(self.stage2.data_ptr())))
+            e3 = sC.record_event()
+        with torch.cuda.stream(sX):
+            sX.wait_event(e3)
+            self._copies2(sX)
+            self.barrier()
+            e4 = sX.record_event()
+        return self.result.view(self.M, self.Lloc), e4
+
+
 class PipelinedRankGeMKM:
-    """The same product with the rows cut into `parts` independent slices, each a RankGeMKM
-    of its own on its own stream, and each handle sized for 1/parts of the SMs.
+    """The same product with the rows cut into `parts` independent slices, each a rank object
+    of its own with its own streams, buffers and communicator.
 
-    Why: in a column-sharded step two of the four passes stream their output to the peers
-    and are bound by NVLink, the other two are bound by arithmetic.  Rows are independent,
-    so while one slice is in an NVLink-bound pass another slice can use the idle FP32 pipes.
-    The slices start one after the other; the GPU's scheduler interleaves their kernels."""
+    Why: two of the four passes of a column-sharded step hand their output to the peers and
+    are bound by NVLink, the other two by arithmetic.  Rows are independent, so one slice's
+    transfers can overlap another slice's arithmetic.
+      mode "staged": kernels fill local per-destination blocks, copy engines ship them
+                     (large-factor shapes); compute kernels run at full width.
+      mode "fused" : the producing kernels store straight into the peers (any shape); the
+                     slices share the SMs (1/parts each) and start staggered."""
 
-    def __init__(self, M, ps, qs, parts=2, group=None):
+    def __init__(self, M, ps, qs, parts=2, group=None, mode="staged"):
         import torch
+        import torch.distributed as dist
         self.torch = torch
         self.parts = parts if M % parts == 0 else 1
+        self.mode = mode
         self.M, self.Mp = int(M), int(M) // self.parts
         self.streams = [torch.cuda.Stream() for _ in range(self.parts)]
         self.slices = []
-        import torch.distributed as dist
         for i, s in enumerate(self.streams):
             # a communicator of its own per slice: barriers of different slices must not
             # queue behind one another on a shared collective stream
@@ -184,41 +282,50 @@ class PipelinedRankGeMKM:
             if dist.is_initialized() and dist.get_world_size(group) > 1 and i > 0:
                 g = dist.new_group(ranks=list(range(dist.get_world_size())))
             with torch.cuda.stream(s):
-                r = RankGeMKM(self.Mp, ps, qs, group=g)
+                cls = StagedRankGeMKM if mode == "staged" else RankGeMKM
+                r = cls(self.Mp, ps, qs, group=g)
                 r.h.set_stream(s)
-                r.lib.fkbSetSmShare(r.h.h, ctypes.c_float(1.0 / self.parts))
+                if mode == "fused":
+                    r.lib.fkbSetSmShare(r.h.h, ctypes.c_float(1.0 / self.parts))
                 self.slices.append(r)
         self.world, self.rank = self.slices[0].world, self.slices[0].rank
         self.Lloc = self.slices[0].Lloc
+        self._done = [None] * self.parts
         torch.cuda.synchronize()
 
     def run(self, x, fs, join=True):
-        """x: this rank's [M, K/G] block.  Returns the list of per-slice result blocks
-        ([M/parts, L/G] each, in row order).
-
-        Slice i+1 starts its local passes when slice i has finished its own, so that one
-        slice's arithmetic-bound passes run beside the other's NVLink-bound ones.  With
-        join=True the caller's stream waits for all slices before and after; join=False
-        leaves the slices free-running from one call to the next (call `join()` before
-        reading the results) so that the stagger carries over between consecutive calls."""
+        """x: this rank's [M, K/G] block.  Returns the per-slice result blocks ([M/parts, L/G]
+        each, in row order).  join=False leaves the slices free-running from one call to the
+        next (call join() before reading results), which keeps them out of phase."""
         torch = self.torch
         cur = torch.cuda.current_stream()
         xs = x.view(self.M, -1)
         outs = []
         if join:
-            for s in self.streams:
+            for r, s in zip(self.slices, self.streams):
                 s.wait_stream(cur)
+                if self.mode == "staged" and r.world > 1:
+                    r.copy_stream.wait_stream(cur)
         if self.world == 1:
             for i, (r, s) in enumerate(zip(self.slices, self.streams)):
                 with torch.cuda.stream(s):
-                    outs.append(r.run(xs[i * self.Mp:(i + 1) * self.Mp], fs))
+                    outs.append(RankGeMKM.run(r, xs[i * self.Mp:(i + 1) * self.Mp], fs))
+            if join:
+                self.join()
+            return outs
+        if self.mode == "staged":
+            prev = None
+            for i, r in enumerate(self.slices):
+                z, done = r.run(xs[i * self.Mp:(i + 1) * self.Mp], fs, after=prev)
+                prev = r.local_done
+                self._done[i] = done
+                outs.append(z)
             if join:
                 self.join()
             return outs
         n = len(self.slices[0].ps)
         L = self.slices[0].lib
         F = _lib.ptrarr([f.data_ptr() for f in fs])
-        # every rank issues the same sequence of kernels and barriers, slice after slice
         prev_local_done = None
         for i, (r, s) in enumerate(zip(self.slices, self.streams)):
             with torch.cuda.stream(s):
@@ -249,8 +356,10 @@ class PipelinedRankGeMKM:
 
     def join(self):
         cur = self.torch.cuda.current_stream()
-        for s in self.streams:
+        for r, s in zip(self.slices, self.streams):
             cur.wait_stream(s)
+            if self.mode == "staged" and r.world > 1:
+                cur.wait_stream(r.copy_stream)
 
     def close(self):
         for r in self.slices:

@@ -42,7 +42,8 @@ def run(args, CONFIGS, B):
     Kl, Ll = K // world, Lc // world
 
     parts = int(os.environ.get("FASTKRON_MG_PARTS", "2"))
-    eng = mg.PipelinedRankGeMKM(M, ps, qs, parts=parts)
+    mode = os.environ.get("FASTKRON_MG_MODE", "staged")
+    eng = mg.PipelinedRankGeMKM(M, ps, qs, parts=parts, mode=mode)
     x = torch.empty(M * Kl, dtype=torch.float32, device="cuda")
     _fill_block(x, c, M, K, Kl, rank)
     fs = [torch.from_numpy(synth.uniform(c["seed"] + 2000 + i, p * q, np.float32)).cuda()
@@ -140,8 +141,10 @@ def run(args, CONFIGS, B):
                     "h2d_bytes_per_step": M * Kl * 4 * world, "d2h_bytes_per_step": M * Ll * 4 * world,
                     "ms_per_step": e2e_ms, "steps": e2e_steps},
             "cpu_baseline": None, "parity_rows_max_rel_err": check,
-            "row_slices": eng.parts, "exchange": "2 all-to-alls per step, fused into the producing kernels as NVLink peer stores; "
-                        "barriers = 1-element NCCL all-reduce on the compute stream",
+            "row_slices": eng.parts, "exchange_mode": eng.mode,
+            "exchange": ("2 all-to-alls per step; staged: kernels fill local per-destination blocks, copy engines "
+                         "ship them over NVLink; fused: the producing kernels store into the peers; barriers = "
+                         "1-element NCCL all-reduce, stream-ordered"),
         }
         print(json.dumps(out), flush=True)
     eng.close()
