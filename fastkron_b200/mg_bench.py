@@ -41,8 +41,11 @@ def run(args, CONFIGS, B):
     Lc = int(np.prod(qs, dtype=object))
     Kl, Ll = K // world, Lc // world
 
-    parts = int(os.environ.get("FASTKRON_MG_PARTS", "2"))
-    mode = os.environ.get("FASTKRON_MG_MODE", "staged")
+    # Transport chosen from measurements on this pool (8 B200 on NVSwitch): at 4 and 8 ranks the
+    # copy-engine exchange with two staggered row slices wins (8 ranks: 7.2 ms against 9.5 ms per
+    # step); at 2 ranks half of every block stays local and storing straight from the kernels wins.
+    mode = os.environ.get("FASTKRON_MG_MODE", "staged" if world >= 4 else "fused")
+    parts = int(os.environ.get("FASTKRON_MG_PARTS", "2" if mode == "staged" else "1"))
     eng = mg.PipelinedRankGeMKM(M, ps, qs, parts=parts, mode=mode)
     x = torch.empty(M * Kl, dtype=torch.float32, device="cuda")
     _fill_block(x, c, M, K, Kl, rank)
