@@ -86,7 +86,10 @@ struct alignas(W * sizeof(T)) VecW {
 // outputs (64 floats / 32 doubles), i.e. kAcc/P whole fibres.
 template <typename T>
 struct StepShape {
-  static constexpr int kAcc = 256 / (int)sizeof(T);
+#ifndef FKB_TILE_ACC_BYTES
+#define FKB_TILE_ACC_BYTES 256
+#endif
+  static constexpr int kAcc = FKB_TILE_ACC_BYTES / (int)sizeof(T);
 };
 template <typename T, int P>
 __host__ __device__ constexpr int stepFibres() { return StepShape<T>::kAcc / P > 0 ? StepShape<T>::kAcc / P : 1; }

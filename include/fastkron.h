@@ -111,123 +111,98 @@ fastKronError gekmmSizes(fastKronHandle handle, uint32_t M, uint32_t N,
                          uint32_t Ps[], uint32_t Qs[],
                          size_t* yElems, size_t* tmpElems);
 
-/* ---- GeMKM (reference: include/fastkron.h:284-296) ------------------------
- * Fs is a HOST array of N device pointers.  temp1 must not be NULL.  temp2 may
- * be NULL unless Z aliases Y or Z is smaller than a temporary; with temp2 NULL
- * the library uses Z itself as its second scratch buffer.  X and Fs are never
- * written.  The call enqueues work on the handle's stream and returns. */
-fastKronError sgemkm(fastKronHandle handle, fastKronBackend backend,
-                     uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
-                     const float* X, fastKronOp opX,
-                     const float* const Fs[], fastKronOp opFs,
-                     float* Z, float alpha, float beta,
-                     const float* Y, float* temp1, float* temp2);
-fastKronError dgemkm(fastKronHandle handle, fastKronBackend backend,
-                     uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
-                     const double* X, fastKronOp opX,
-                     const double* const Fs[], fastKronOp opFs,
-                     double* Z, double alpha, double beta,
-                     const double* Y, double* temp1, double* temp2);
+/* The argument lists of the product functions differ only in the element type, so they
+ * are written once as macros (T = float for the s-, double for the d- functions).
+ * Order and meaning are the reference's.  Common rules: Fs is a HOST array of N device
+ * pointers; X and Fs are never written; calls enqueue work on the handle's stream and
+ * return without synchronising. */
 
-/* ---- GeKMM (reference: include/fastkron.h:329-341); note Qs before Ps ----- */
-fastKronError sgekmm(fastKronHandle handle, fastKronBackend backend,
-                     uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
-                     const float* const Fs[], fastKronOp opFs,
-                     const float* X, fastKronOp opX,
-                     float* Z, float alpha, float beta,
-                     const float* Y, float* temp1, float* temp2);
-fastKronError dgekmm(fastKronHandle handle, fastKronBackend backend,
-                     uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
-                     const double* const Fs[], fastKronOp opFs,
-                     const double* X, fastKronOp opX,
-                     double* Z, double alpha, double beta,
-                     const double* Y, double* temp1, double* temp2);
+/* GeMKM arguments (reference: include/fastkron.h:284-296): M rows, N factors of shape
+ * Ps[i] x Qs[i]; temp1 must not be NULL; temp2 may be NULL unless Z aliases Y or Z is
+ * smaller than a temporary -- with temp2 NULL the library uses Z as its second scratch. */
+#define FASTKRON_GEMKM_ARGS(T)                                                    \
+  fastKronHandle handle, fastKronBackend backend,                                 \
+  uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],                           \
+  const T* X, fastKronOp opX, const T* const Fs[], fastKronOp opFs,               \
+  T* Z, T alpha, T beta, const T* Y, T* temp1, T* temp2
 
-/* ---- strided-batched GeMKM / GeKMM (reference: include/fastkron.h:384-449) -
- * Batch b uses X + b*strideX, Fs[i] + b*strideF[i], Z + b*strideZ,
- * Y + b*strideY (strides in elements; 0 shares the operand across the batch).
- * Each temporary holds batchCount * tmpElems elements. */
-fastKronError sgemkmStridedBatched(fastKronHandle handle, fastKronBackend backend,
-                                   uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
-                                   const float* X, fastKronOp opX, uint64_t strideX,
-                                   const float* const Fs[], fastKronOp opFs, uint64_t strideF[],
-                                   float* Z, uint64_t strideZ, float alpha, float beta,
-                                   uint32_t batchCount, const float* Y, uint64_t strideY,
-                                   float* temp1, float* temp2);
-fastKronError dgemkmStridedBatched(fastKronHandle handle, fastKronBackend backend,
-                                   uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
-                                   const double* X, fastKronOp opX, uint64_t strideX,
-                                   const double* const Fs[], fastKronOp opFs, uint64_t strideF[],
-                                   double* Z, uint64_t strideZ, double alpha, double beta,
-                                   uint32_t batchCount, const double* Y, uint64_t strideY,
-                                   double* temp1, double* temp2);
-fastKronError sgekmmStridedBatched(fastKronHandle handle, fastKronBackend backend,
-                                   uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
-                                   const float* const Fs[], fastKronOp opFs, uint64_t strideF[],
-                                   const float* X, fastKronOp opX, uint64_t strideX,
-                                   float* Z, uint64_t strideZ, float alpha, float beta,
-                                   uint32_t batchCount, const float* Y, uint64_t strideY,
-                                   float* temp1, float* temp2);
-fastKronError dgekmmStridedBatched(fastKronHandle handle, fastKronBackend backend,
-                                   uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
-                                   const double* const Fs[], fastKronOp opFs, uint64_t strideF[],
-                                   const double* X, fastKronOp opX, uint64_t strideX,
-                                   double* Z, uint64_t strideZ, double alpha, double beta,
-                                   uint32_t batchCount, const double* Y, uint64_t strideY,
-                                   double* temp1, double* temp2);
+/* GeKMM arguments (reference: include/fastkron.h:329-341); note Qs before Ps and the
+ * factors before X. */
+#define FASTKRON_GEKMM_ARGS(T)                                                    \
+  fastKronHandle handle, fastKronBackend backend,                                 \
+  uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,                           \
+  const T* const Fs[], fastKronOp opFs, const T* X, fastKronOp opX,               \
+  T* Z, T alpha, T beta, const T* Y, T* temp1, T* temp2
 
-/* ---- forward variants keeping every intermediate
- *      (reference: include/fastkron.h:470-628) --------------------------------
- * alpha = 1, beta = 0.  Intermediates[i-1] receives the matrix obtained after
- * the factors N-1 .. i have been applied (i = N-1 .. 1), in the reference's
- * sliced-multiply column order; its element count is intermediateElems[i-1]. */
+fastKronError sgemkm(FASTKRON_GEMKM_ARGS(float));
+fastKronError dgemkm(FASTKRON_GEMKM_ARGS(double));
+fastKronError sgekmm(FASTKRON_GEKMM_ARGS(float));
+fastKronError dgekmm(FASTKRON_GEKMM_ARGS(double));
+
+/* Strided-batched forms (reference: include/fastkron.h:384-449).  Batch b uses
+ * X + b*strideX, Fs[i] + b*strideF[i], Z + b*strideZ, Y + b*strideY (strides in elements;
+ * 0 shares the operand across the batch).  Each temporary holds batchCount * tmpElems. */
+#define FASTKRON_GEMKM_SB_ARGS(T)                                                 \
+  fastKronHandle handle, fastKronBackend backend,                                 \
+  uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],                           \
+  const T* X, fastKronOp opX, uint64_t strideX,                                   \
+  const T* const Fs[], fastKronOp opFs, uint64_t strideF[],                       \
+  T* Z, uint64_t strideZ, T alpha, T beta, uint32_t batchCount,                   \
+  const T* Y, uint64_t strideY, T* temp1, T* temp2
+#define FASTKRON_GEKMM_SB_ARGS(T)                                                 \
+  fastKronHandle handle, fastKronBackend backend,                                 \
+  uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,                           \
+  const T* const Fs[], fastKronOp opFs, uint64_t strideF[],                       \
+  const T* X, fastKronOp opX, uint64_t strideX,                                   \
+  T* Z, uint64_t strideZ, T alpha, T beta, uint32_t batchCount,                   \
+  const T* Y, uint64_t strideY, T* temp1, T* temp2
+
+fastKronError sgemkmStridedBatched(FASTKRON_GEMKM_SB_ARGS(float));
+fastKronError dgemkmStridedBatched(FASTKRON_GEMKM_SB_ARGS(double));
+fastKronError sgekmmStridedBatched(FASTKRON_GEKMM_SB_ARGS(float));
+fastKronError dgekmmStridedBatched(FASTKRON_GEKMM_SB_ARGS(double));
+
+/* Forward variants keeping every intermediate (reference: include/fastkron.h:470-628):
+ * alpha = 1, beta = 0.  Intermediates[i-1] receives the matrix obtained after the factors
+ * N-1 .. i have been applied (i = N-1 .. 1), in the reference's sliced-multiply column
+ * order; gekmmSizesForward reports its element count in intermediateElems[i-1]. */
 fastKronError gekmmSizesForward(fastKronHandle handle, uint32_t M, uint32_t N,
                                 uint32_t Ps[], uint32_t Qs[],
                                 size_t* yElems, size_t* intermediateElems);
-fastKronError smkmForward(fastKronHandle handle, fastKronBackend backend,
-                          uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
-                          const float* X, fastKronOp opX,
-                          const float* const Fs[], fastKronOp opFs,
-                          float* Z, float* Intermediates[]);
-fastKronError dmkmForward(fastKronHandle handle, fastKronBackend backend,
-                          uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
-                          const double* X, fastKronOp opX,
-                          const double* const Fs[], fastKronOp opFs,
-                          double* Z, double* Intermediates[]);
-fastKronError skmmForward(fastKronHandle handle, fastKronBackend backend,
-                          uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
-                          const float* const Fs[], fastKronOp opFs,
-                          const float* X, fastKronOp opX,
-                          float* Z, float* Intermediates[]);
-fastKronError dkmmForward(fastKronHandle handle, fastKronBackend backend,
-                          uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
-                          const double* const Fs[], fastKronOp opFs,
-                          const double* X, fastKronOp opX,
-                          double* Z, double* Intermediates[]);
-fastKronError smkmForwardStridedBatched(fastKronHandle handle, fastKronBackend backend,
-                                        uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
-                                        const float* X, fastKronOp opX, uint64_t strideX,
-                                        const float* const Fs[], fastKronOp opFs, uint64_t strideF[],
-                                        float* Z, uint64_t strideZ, uint32_t batchCount,
-                                        float* Intermediates[], uint64_t strideIntermediates[]);
-fastKronError dmkmForwardStridedBatched(fastKronHandle handle, fastKronBackend backend,
-                                        uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],
-                                        const double* X, fastKronOp opX, uint64_t strideX,
-                                        const double* const Fs[], fastKronOp opFs, uint64_t strideF[],
-                                        double* Z, uint64_t strideZ, uint32_t batchCount,
-                                        double* Intermediates[], uint64_t strideIntermediates[]);
-fastKronError skmmForwardStridedBatched(fastKronHandle handle, fastKronBackend backend,
-                                        uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
-                                        const float* const Fs[], fastKronOp opFs, uint64_t strideF[],
-                                        const float* X, fastKronOp opX, uint64_t strideX,
-                                        float* Z, uint64_t strideZ, uint32_t batchCount,
-                                        float* Intermediates[], uint64_t strideIntermediates[]);
-fastKronError dkmmForwardStridedBatched(fastKronHandle handle, fastKronBackend backend,
-                                        uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,
-                                        const double* const Fs[], fastKronOp opFs, uint64_t strideF[],
-                                        const double* X, fastKronOp opX, uint64_t strideX,
-                                        double* Z, uint64_t strideZ, uint32_t batchCount,
-                                        double* Intermediates[], uint64_t strideIntermediates[]);
+
+#define FASTKRON_MKM_FWD_ARGS(T)                                                  \
+  fastKronHandle handle, fastKronBackend backend,                                 \
+  uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],                           \
+  const T* X, fastKronOp opX, const T* const Fs[], fastKronOp opFs,               \
+  T* Z, T* Intermediates[]
+#define FASTKRON_KMM_FWD_ARGS(T)                                                  \
+  fastKronHandle handle, fastKronBackend backend,                                 \
+  uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,                           \
+  const T* const Fs[], fastKronOp opFs, const T* X, fastKronOp opX,               \
+  T* Z, T* Intermediates[]
+#define FASTKRON_MKM_FWD_SB_ARGS(T)                                               \
+  fastKronHandle handle, fastKronBackend backend,                                 \
+  uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],                           \
+  const T* X, fastKronOp opX, uint64_t strideX,                                   \
+  const T* const Fs[], fastKronOp opFs, uint64_t strideF[],                       \
+  T* Z, uint64_t strideZ, uint32_t batchCount,                                    \
+  T* Intermediates[], uint64_t strideIntermediates[]
+#define FASTKRON_KMM_FWD_SB_ARGS(T)                                               \
+  fastKronHandle handle, fastKronBackend backend,                                 \
+  uint32_t N, uint32_t Qs[], uint32_t Ps[], uint32_t M,                           \
+  const T* const Fs[], fastKronOp opFs, uint64_t strideF[],                       \
+  const T* X, fastKronOp opX, uint64_t strideX,                                   \
+  T* Z, uint64_t strideZ, uint32_t batchCount,                                    \
+  T* Intermediates[], uint64_t strideIntermediates[]
+
+fastKronError smkmForward(FASTKRON_MKM_FWD_ARGS(float));
+fastKronError dmkmForward(FASTKRON_MKM_FWD_ARGS(double));
+fastKronError skmmForward(FASTKRON_KMM_FWD_ARGS(float));
+fastKronError dkmmForward(FASTKRON_KMM_FWD_ARGS(double));
+fastKronError smkmForwardStridedBatched(FASTKRON_MKM_FWD_SB_ARGS(float));
+fastKronError dmkmForwardStridedBatched(FASTKRON_MKM_FWD_SB_ARGS(double));
+fastKronError skmmForwardStridedBatched(FASTKRON_KMM_FWD_SB_ARGS(float));
+fastKronError dkmmForwardStridedBatched(FASTKRON_KMM_FWD_SB_ARGS(double));
 
 /* ---- GeMKM without caller-provided temporaries -------------------------------------
  * This function has no counterpart in the reference.  It is sgemkm for callers that
