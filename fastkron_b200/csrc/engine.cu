@@ -131,12 +131,42 @@ fastKronError Engine::run(Problem pr, const CallOperands& ops) {
   }
   po.align = al;
 
+  // A batch of GeMKMs that shares its factors and whose X, Z (and Y) entries lie back to
+  // back is one GeMKM with batch*M rows: rows are independent.  (The reference launches
+  // its kernels with a batch grid dimension instead, src/kernels/gpu_kmmkernel.h:124-144.)
+  if (pr.batch > 1 && pr.mm == MMType::MKM && pr.opX == fastKronOp_N && !pr.forward && ops.strideF &&
+      (uint64_t)pr.M * pr.batch < (1ull << 32)) {
+    bool shared = true;
+    for (uint32_t i = 0; i < pr.N; i++) shared = shared && ops.strideF[i] == 0;
+    const uint64_t K = pr.K(), L = pr.L();
+    if (shared && ops.strideX == (uint64_t)pr.M * K && ops.strideZ == (uint64_t)pr.M * L &&
+        (ops.beta == 0.0 || ops.strideY == (uint64_t)pr.M * L)) {
+      Problem folded = pr;
+      folded.M = pr.M * pr.batch;
+      folded.batch = 1;
+      return run(folded, ops);
+    }
+  }
+
   const std::string key = planKey(pr, po);
   auto it = planCache_.find(key);
   if (it == planCache_.end()) {
     Plan plan;
     fastKronError e = makePlan(pr, po, &plan);
     if (e != fastKronSuccess) return e;
+    // fastKronOptionsTune: time the candidate plans once on the caller's own buffers (X and
+    // the factors are never written; Z and the temporaries are scratch until the real run)
+    // and keep the fastest.  Skipped when Z aliases Y, whose contents the trial runs would
+    // destroy.  (Role of the reference's Autotuner::tune, src/autotuner/autotuner.cpp:24-328.)
+    if ((options_ & fastKronOptionsTune) != 0 && pr.batch == 1 && (const void*)ops.Z != ops.Y) {
+      PlanOptions alt = po;
+      alt.fusion = !po.fusion;
+      Plan other;
+      if (makePlan(pr, alt, &other) == fastKronSuccess && other.passes.size() != plan.passes.size()) {
+        const float tA = timePlan(pr, plan, ops), tB = timePlan(pr, other, ops);
+        if (tB > 0.f && tA > 0.f && tB < tA) plan = other;
+      }
+    }
     it = planCache_.emplace(key, std::move(plan)).first;
   }
   const Plan& plan = it->second;
@@ -167,6 +197,25 @@ fastKronError Engine::run(Problem pr, const CallOperands& ops) {
     if (e != fastKronSuccess) return e;
   }
   return fastKronSuccess;
+}
+
+// Average device time (ms) of a plan over three runs after one warm-up; negative on failure.
+float Engine::timePlan(const Problem& pr, const Plan& plan, const CallOperands& ops) {
+  cudaEvent_t a, b;
+  if (cudaEventCreate(&a) != cudaSuccess) return -1.f;
+  if (cudaEventCreate(&b) != cudaSuccess) { cudaEventDestroy(a); return -1.f; }
+  float ms = -1.f;
+  if (execute(pr, plan, ops, stream_, smCount()) == fastKronSuccess) {
+    cudaEventRecord(a, stream_);
+    bool ok = true;
+    for (int i = 0; i < 3 && ok; i++) ok = execute(pr, plan, ops, stream_, smCount()) == fastKronSuccess;
+    cudaEventRecord(b, stream_);
+    if (ok && cudaEventSynchronize(b) == cudaSuccess && cudaEventElapsedTime(&ms, a, b) == cudaSuccess) ms /= 3.f;
+    else ms = -1.f;
+  }
+  cudaEventDestroy(a);
+  cudaEventDestroy(b);
+  return ms;
 }
 
 // One kernel launch: the pass's own kernel family, the generic kernel when that family

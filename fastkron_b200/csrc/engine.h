@@ -69,6 +69,8 @@ class Engine {
   fastKronError execute(const Problem& pr, const Plan& plan, const CallOperands& ops,
                         cudaStream_t stream, int smCount);
 
+  float timePlan(const Problem& pr, const Plan& plan, const CallOperands& ops);
+
   // Launch one pass (with fallback to the generic kernel and optional event timing).
   fastKronError launchPass(const Pass& ps, const LaunchCtx& cx);
 
