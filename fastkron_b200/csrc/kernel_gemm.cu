@@ -2,7 +2,53 @@
 #include "kernel_gemm.cuh"
 #include "gemm_table.h"
 
+#include <string.h>
+
+#include <stdlib.h>
+
 namespace fkb {
+
+// cuTensorMapEncodeTiled from the driver, without linking libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn tensorMapEncoder() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// TMA staging is on unless FASTKRON_GEMM_TMA=0.
+static bool tmaWanted() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("FASTKRON_GEMM_TMA"); v = (e && e[0] == '0') ? 0 : 1; }
+  return v == 1;
+}
+
+// Tensor map over the pass input viewed as [chunks][P][B], box = one stage [1][PC][TJ].
+template <typename T>
+static bool encodeInputMap(CUtensorMap* tm, const void* X, unsigned long long chunks, unsigned P, unsigned long long B,
+                           unsigned TJ, unsigned PC) {
+  EncodeTiledFn enc = tensorMapEncoder();
+  if (!enc || B > 0xFFFFFFFFull || chunks > 0xFFFFFFFFull || (B * sizeof(T)) % 16 != 0) return false;
+  const cuuint64_t dims[3] = {B, P, chunks};
+  const cuuint64_t strides[2] = {B * sizeof(T), (cuuint64_t)P * B * sizeof(T)};
+  const cuuint32_t box[3] = {TJ, PC, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = sizeof(T) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT64;
+  return enc(tm, dt, 3, const_cast<void*>(X), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 bool gemmSupported(DType dt, uint32_t P, uint32_t Q, uint64_t B) { return gemmEligible(dt, P, Q, B); }
 
@@ -36,13 +82,19 @@ static fastKronError launchGemmOne(const Pass& ps, const LaunchCtx& cx, int mode
     if (e != cudaSuccess || n < 1) return e != cudaSuccess ? cudaToFk(e) : fastKronKernelNotFound;
     ctasPerSm = n;
   }
+  CUtensorMap tmap;
+  memset(&tmap, 0, sizeof(tmap));
+  a.useTma = 0;
+  if (!XT && mode == 0 && a.pSplit == 0 && tmaWanted() && TJ <= 256 && PC <= 256 &&
+      encodeInputMap<T>(&tmap, a.X, a.numChunks, P, a.B, TJ, PC))
+    a.useTma = 1;
   unsigned long long grid = (unsigned long long)cx.smCount * ctasPerSm;
   if (cx.tilesPerCta > 0) {
     const unsigned long long want = (a.numTiles + cx.tilesPerCta - 1) / cx.tilesPerCta;
     if (want > grid) grid = want;
   }
   if (grid > a.numTiles) grid = a.numTiles;
-  kern<<<(unsigned)grid, C::THREADS, C::SMEM, cx.stream>>>(a);
+  kern<<<(unsigned)grid, C::THREADS, C::SMEM, cx.stream>>>(a, tmap);
   return cudaToFk(cudaGetLastError());
 }
 
@@ -79,4 +131,13 @@ fastKronError launchGemm(const Pass& ps, const LaunchCtx& cx) {
   return fastKronKernelNotFound;
 }
 
+int gemmTmaTimeouts() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, gGemmTmaTimeouts, sizeof(int)) != cudaSuccess) { cudaGetLastError(); return -1; }
+  return v;
+}
+
 }  // namespace fkb
+
+// Non-zero if a bounded wait on a TMA stage barrier ever gave up in this process (tests).
+extern "C" int fkbGemmTmaTimeouts() { return fkb::gemmTmaTimeouts(); }

@@ -3,8 +3,10 @@
 // written as a register-blocked FFMA/DFMA GEMM  C[q, j] = sum_p F[p, q] * X[p, j]
 // where j runs over TJ trailing positions (or, when B is small, over several whole
 // chunks).  The factor stays resident in shared memory for the life of the
-// (persistent) CTA; X streams through a ring of cp.async stages, PC rows of p at a
-// time, so the global loads of tile t+1 overlap the arithmetic of tile t.  Every
+// (persistent) CTA; X streams through a ring of stages, PC rows of p at a time, so the
+// global loads of tile t+1 overlap the arithmetic of tile t.  A stage is filled by one
+// TMA instruction (cp.async.bulk.tensor.3d, completion on an mbarrier) in the main tile
+// mode and by 16-byte cp.async from every thread in the others.  Every
 // thread owns an MQ x MJ block of outputs whose rows/columns are spread in 16-byte
 // groups so that both the shared-memory operand reads and the global stores are
 // 128-bit and conflict free: a warp is 4 (q) x 8 (j) lanes, so a factor read touches
@@ -18,6 +20,8 @@
 // (src/kernels/cuda/kernel.cuh:53-224): products accumulated over p ascending,
 // alpha/beta applied by the pass that consumes factor 0.
 #pragma once
+
+#include <cuda.h>            // CUtensorMap (type only; the encoder is fetched at run time)
 
 #include "kernels.h"
 #include "kernel_tile.cuh"   // Vec16, cpAsync16
@@ -41,7 +45,45 @@ struct GemmArgs {
   // (Input of the multi-GPU phase 2, received as [sender][M][P/G][B].)
   unsigned pSplit = 0;
   unsigned long long pOuter = 0, nStride = 0;
+  // mode 0 without split input: stages are filled by TMA (cp.async.bulk.tensor, one
+  // instruction per stage issued by one thread, completion on an mbarrier) instead of
+  // 16-byte cp.async from every thread.
+  int useTma = 0;
 };
+
+// ---- mbarrier / TMA primitives (sm_90+ PTX; no multicast, one CTA) ---------------------
+__device__ int gGemmTmaTimeouts = 0;     // set when a bounded wait on a stage barrier gave up
+
+__device__ __forceinline__ void mbarInit(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"((unsigned)__cvta_generic_to_shared(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbarInitFence() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
+__device__ __forceinline__ void mbarExpectTx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"((unsigned)__cvta_generic_to_shared(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbarTryWait(unsigned long long* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"((unsigned)__cvta_generic_to_shared(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Wait for a stage; gives up after about two seconds, records that and reports failure.
+__device__ __forceinline__ bool mbarWaitBounded(unsigned long long* bar, unsigned parity) {
+  if (mbarTryWait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbarTryWait(bar, parity)) {
+    if (clock64() - t0 > 4000000000ll) { atomicExch(&gGemmTmaTimeouts, 1); return false; }
+  }
+  return true;
+}
+__device__ __forceinline__ void tmaLoad3D(void* smemDst, const CUtensorMap* tmap, int x, int y, int z,
+                                          unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+      ::"r"((unsigned)__cvta_generic_to_shared(smemDst)), "l"(tmap), "r"(x), "r"(y), "r"(z),
+        "r"((unsigned)__cvta_generic_to_shared(bar)) : "memory");
+}
 
 // Pointer to output row (chunk n, row q), trailing position 0.
 template <typename T, int Q>
@@ -75,7 +117,7 @@ struct GemmCfg {
 
 template <typename T, int P, int Q, int TJ, int PC, int STAGES, int MQ, int MJ, bool XT, int UNR = 8, int MINB = 0>
 __global__ void __launch_bounds__((Q / MQ) * (TJ / MJ), (MINB > 0 ? MINB : ((Q / MQ) * (TJ / MJ) <= 256 ? 2 : 1)))
-gemmPassKernel(const GemmArgs<T> a) {
+gemmPassKernel(const GemmArgs<T> a, const __grid_constant__ CUtensorMap tmap) {
   using C = GemmCfg<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT>;
   using V = Vec16<T>;
   constexpr int VEC = C::VEC, THREADS = C::THREADS, NGQ = C::NGQ, NGJ = C::NGJ;
@@ -86,8 +128,15 @@ gemmPassKernel(const GemmArgs<T> a) {
   extern __shared__ __align__(1024) unsigned char smemRaw[];
   T* Fs = reinterpret_cast<T*>(smemRaw);
   T* stages = Fs + P * Q;
+  __shared__ __align__(8) unsigned long long fullBar[STAGES];
 
   const int tid = threadIdx.x;
+  const bool tma = !XT && a.useTma != 0;
+  if (tma && tid == 0) {
+#pragma unroll
+    for (int i = 0; i < STAGES; i++) mbarInit(&fullBar[i], 1);
+    mbarInitFence();
+  }
   const int lane = tid & 31, warp = tid >> 5;
   const int tq = (warp % C::NWQ) * 4 + (lane & 3);
   const int tj = (warp / C::NWQ) * 8 + (lane >> 2);
@@ -143,7 +192,12 @@ gemmPassKernel(const GemmArgs<T> a) {
     if constexpr (!XT) {
       if (a.mode == 0) {
         const unsigned n = isTile / tpc, bt = isTile - n * tpc;
-        if (a.pSplit == 0) {
+        if (tma) {
+          if (tid == 0) {
+            mbarExpectTx(&fullBar[isSlot], (unsigned)(C::STAGE_ELEMS * sizeof(T)));
+            tmaLoad3D(stages + (size_t)isSlot * C::STAGE_ELEMS, &tmap, (int)(bt * TJ), isC * PC, (int)n, &fullBar[isSlot]);
+          }
+        } else if (a.pSplit == 0) {
           const T* src = a.X + n * PB + (unsigned long long)bt * TJ + (unsigned long long)isC * PC * a.B + ldOff;
 #pragma unroll
           for (int i = 0; i < NLD; i++) { cpAsync16(dst, src); dst += ldSmemStep; src += ldStep; }
@@ -194,8 +248,14 @@ gemmPassKernel(const GemmArgs<T> a) {
   unsigned curTile = first;
   int c = 0;
   unsigned slot = 0;
+  unsigned phases = 0;                 // bit i: parity of the next completion of fullBar[i]
   for (unsigned s = 0; s < total; s++) {
-    cpAsyncWait<STAGES - 2>();
+    if (tma) {
+      if (!mbarWaitBounded(&fullBar[slot], (phases >> slot) & 1u)) return;
+      phases ^= 1u << slot;
+    } else {
+      cpAsyncWait<STAGES - 2>();
+    }
     __syncthreads();
     if (s + STAGES - 1 < total) issue();
     cpAsyncCommit();

@@ -9,6 +9,7 @@
 // (The role of the reference's run-time autotuner, src/autotuner/autotuner.cpp:24-328, for
 // this kernel family: measurement happens once, offline.)
 #include <cstdio>
+#include <cstring>
 #include <vector>
 
 #include "kernel_gemm.cuh"
@@ -38,12 +39,14 @@ static void runVariant(const char* name, const T* X, T* Z, const T* F, unsigned 
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
   unsigned long long grid = (unsigned long long)sms * occ;
   if (grid > a.numTiles) grid = a.numTiles;
+  CUtensorMap dummyMap;
+  memset(&dummyMap, 0, sizeof(dummyMap));     // this tool measures the cp.async staging
   cudaEvent_t e0, e1;
   cudaEventCreate(&e0); cudaEventCreate(&e1);
   float best = 1e9f;
   for (int it = 0; it < 6; it++) {
     cudaEventRecord(e0);
-    kern<<<(unsigned)grid, C::THREADS, C::SMEM>>>(a);
+    kern<<<(unsigned)grid, C::THREADS, C::SMEM>>>(a, dummyMap);
     cudaEventRecord(e1); cudaEventSynchronize(e1);
     float ms; cudaEventElapsedTime(&ms, e0, e1);
     if (it >= 2 && ms < best) best = ms;

@@ -113,6 +113,9 @@ def test_large_factor_kernels(h, c):
     x, fs, y = cases.operands(c)
     z = gpu_util.run_case(h, c, x=x, fs=fs, y=y)
     assert cases.row_rel_err(z, oracle_z(c, x, fs, y), c["mm"]) <= cases.TOL[c["dt"]]
+    # the TMA-staged tile mode waits on its stage barriers with a time limit; it must never trip
+    from fastkron_b200 import lib as fk
+    assert fk.get().fkbGemmTmaTimeouts() == 0
 
 
 def test_fusion_off_matches_fusion_on(h):
