@@ -21,6 +21,7 @@
 #include "gemm_table.h"
 
 #include <sstream>
+#include <stdlib.h>
 
 namespace fkb {
 
@@ -52,6 +53,8 @@ static TileChoice chooseTile(DType dt, uint32_t P, int avail, uint64_t B, bool f
   const bool wide = B > 1;
   if (!fusion) avail = 1;
   if (avail > kMaxGroup) avail = kMaxGroup;
+  // FASTKRON_MAX_FUSE caps the fusion depth (tuning / experiments)
+  if (const char* cap = getenv("FASTKRON_MAX_FUSE")) { const int c2 = atoi(cap); if (c2 >= 1 && c2 < avail) avail = c2; }
   if (wide) {
     const uint64_t W = 128 / es;
     if (B % W != 0) return c;
@@ -67,6 +70,15 @@ static TileChoice chooseTile(DType dt, uint32_t P, int avail, uint64_t B, bool f
       uint64_t g = 1; for (int k = 0; k < nf; k++) g *= P;
       if (g * es <= 32 * 1024 && (g * es) % 16 == 0) { c.nf = nf; break; }
     }
+  }
+  // Balance: when the run of equal factors needs several passes anyway, spread the factors
+  // evenly over them (measured on B200: 16x16^4 as 2+2 beats 3+1, 8x8^8 as 4+2+2 ties 4+3+1),
+  // because a pass's time grows with its depth while its memory traffic does not.
+  if (c.nf >= 1 && c.nf < avail) {
+    const int passes = (avail + c.nf - 1) / c.nf;
+    int even = (avail + passes - 1) / passes;
+    while (even >= 1 && !tileInTable(P, even, wide)) even--;
+    if (even >= 1 && even < c.nf) c.nf = even;
   }
   return c;
 }
