@@ -272,8 +272,92 @@ __host__ __device__ __forceinline__ void stepScalar(T* __restrict__ tile, const 
   }
 }
 
+// fp64, P = 8 on the DMMA tensor path (mma.sync.m8n8k4.f64): a warp takes 8 neighbouring
+// fibres at a time, A = the fibres (8 x 8 inputs, two k-steps of 4), B = the factor (held in
+// two registers per lane for the whole step), C = the 8 x 8 outputs.  Per 64 outputs a lane
+// issues 2 loads, 2 MMAs and 2 stores instead of 16 DFMAs plus operand loads; the FP64 tensor
+// rate of B200 equals its DFMA rate (37 TFLOP/s measured for both), so the gain is in issue
+// slots and shared-memory instructions, which is what bounds the SIMT form of this step.
+// A group's inputs are read and its outputs written by the lanes of one warp, and mma.sync
+// orders them, so the in-place update needs no barrier, as in the SIMT steps.
+#if defined(__CUDA_ARCH__)
+__device__ __forceinline__ void dmma884(double& c0, double& c1, double a, double b) {
+  asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};\n"
+               : "+d"(c0), "+d"(c1) : "d"(a), "d"(b));
+}
+template <int S, int THREADS>
+__device__ __forceinline__ void stepDmma8(double* __restrict__ tile, const double* __restrict__ Fs, int E, int tid) {
+  constexpr int P = 8;
+  const int lane = tid & 31, warp = tid >> 5, r = lane >> 2, t = lane & 3;
+  const double b0 = Fs[t * P + r], b1 = Fs[(t + 4) * P + r];
+  const int nfib = E / P;
+  const int ngroups = (nfib + 7) / 8;              // the last group may be partial (tiny tiles)
+  for (int gid = warp; gid < ngroups; gid += THREADS / 32) {
+    const unsigned phi = (unsigned)gid * 8 + r;
+    const bool live = (int)phi < nfib;
+    const unsigned base = (S == 1) ? phi * P : (phi / S) * (unsigned)(S * P) + phi % S;
+    const unsigned pb = physIdx<double>(base);
+    const double a0 = live ? tile[pb ^ physIdx<double>((unsigned)(t * S))] : 0.0;
+    const double a1 = live ? tile[pb ^ physIdx<double>((unsigned)((t + 4) * S))] : 0.0;
+    double c0 = 0.0, c1 = 0.0;
+    dmma884(c0, c1, a0, b0);
+    dmma884(c0, c1, a1, b1);
+    if (!live) continue;
+    if (S == 1) {
+      Vec16<double> o;
+      o.v[0] = c0; o.v[1] = c1;
+      *reinterpret_cast<Vec16<double>*>(tile + (pb ^ physIdx<double>((unsigned)(2 * t)))) = o;
+    } else {
+      tile[pb ^ physIdx<double>((unsigned)(2 * t * S))] = c0;
+      tile[pb ^ physIdx<double>((unsigned)((2 * t + 1) * S))] = c1;
+    }
+  }
+}
+// Two neighbouring modes in one go, the intermediate never leaving registers.  A warp takes
+// an 8 x 8 block X[a][b] (a: the slower mode, stride 8*Sb; b: the faster one, stride Sb).
+//   first  C1t[qb][a]  = sum_b Fb[b][qb] * X[a][b]      A = Fb^T (constant), B = X^T
+//   then   C2t[qb][qa] = sum_a C1t[qb][a] * Fa[a][qa]   A = C1t,            B = Fa (constant)
+// The m8n8k4 C fragment gives lane (r, t) the entries [qb = r][a = 2t, 2t+1]; taking a = 2t
+// as the contraction index of the first k-step and a = 2t+1 of the second (with Fa's rows
+// permuted the same way) makes that fragment directly the A operand: no shuffles.  Shared
+// memory is read and written once per two factors instead of once per factor.
+template <int Sb, int THREADS>
+__device__ __forceinline__ void stepDmma8Pair(double* __restrict__ tile, const double* __restrict__ Fb,
+                                              const double* __restrict__ Fa, int E, int tid) {
+  constexpr int P = 8;
+  constexpr int Sa = Sb * P;
+  const int lane = tid & 31, warp = tid >> 5, r = lane >> 2, t = lane & 3;
+  // first product: A[m = qb = r][k = b = t + 4k'] = Fb[b][qb]
+  const double fb0 = Fb[t * P + r], fb1 = Fb[(t + 4) * P + r];
+  // second product: B[k][n = qa = r], k-step 0 <-> a = 2t, k-step 1 <-> a = 2t + 1
+  const double fa0 = Fa[(2 * t) * P + r], fa1 = Fa[(2 * t + 1) * P + r];
+  const int nblocks = E / (P * P);
+  for (int blk = warp; blk < nblocks; blk += THREADS / 32) {
+    const unsigned lo = (unsigned)blk % Sb, hi = (unsigned)blk / Sb;
+    const unsigned pb = physIdx<double>(hi * (unsigned)(Sa * P) + lo);
+    // B[k = b][n = a = r] = X[a = r][b = t + 4k']
+    const double x0 = tile[pb ^ physIdx<double>((unsigned)(r * Sa + t * Sb))];
+    const double x1 = tile[pb ^ physIdx<double>((unsigned)(r * Sa + (t + 4) * Sb))];
+    double c0 = 0.0, c1 = 0.0;            // C1t[qb = r][a = 2t], [a = 2t + 1]
+    dmma884(c0, c1, fb0, x0);
+    dmma884(c0, c1, fb1, x1);
+    double d0 = 0.0, d1 = 0.0;            // C2t[qb = r][qa = 2t], [qa = 2t + 1]
+    dmma884(d0, d1, c0, fa0);
+    dmma884(d0, d1, c1, fa1);
+    tile[pb ^ physIdx<double>((unsigned)((2 * t) * Sa + r * Sb))] = d0;
+    tile[pb ^ physIdx<double>((unsigned)((2 * t + 1) * Sa + r * Sb))] = d1;
+  }
+}
+#endif
+
 template <typename T, int P, int S, int THREADS>
 __host__ __device__ __forceinline__ void stepDispatch(T* tile, const T* Fs, int E, int tid) {
+#if defined(__CUDA_ARCH__) && !defined(FKB_NO_DMMA)
+  if constexpr (sizeof(T) == 8 && P == 8 && (S == 1 || S % 8 == 0)) {
+    stepDmma8<S, THREADS>(tile, Fs, E, tid);
+    return;
+  }
+#endif
   constexpr int VEC = Vec16<T>::N;
   constexpr int NFIB = stepFibres<T, P>();
   constexpr int W = NFIB < VEC ? NFIB : VEC;
@@ -291,6 +375,15 @@ template <typename T, int P, int NF, int BT, int THREADS, int J>
 struct StepChain {
   static __device__ __forceinline__ void run(T* tile, const T* Fs, int E) {
     constexpr int S = ipow(P, NF - 1 - J) * BT;
+#if defined(__CUDA_ARCH__) && !defined(FKB_NO_DMMA)
+    if constexpr (sizeof(T) == 8 && P == 8 && J >= 1 && (S == 1 || S % 8 == 0)) {
+      // factors J and J-1 together, intermediate in registers
+      stepDmma8Pair<S, THREADS>(tile, Fs + J * P * P, Fs + (J - 1) * P * P, E, (int)threadIdx.x);
+      __syncthreads();
+      StepChain<T, P, NF, BT, THREADS, J - 2>::run(tile, Fs, E);
+      return;
+    }
+#endif
     stepDispatch<T, P, S, THREADS>(tile, Fs + J * P * P, E, (int)threadIdx.x);
     __syncthreads();
     StepChain<T, P, NF, BT, THREADS, J - 1>::run(tile, Fs, E);
@@ -298,6 +391,10 @@ struct StepChain {
 };
 template <typename T, int P, int NF, int BT, int THREADS>
 struct StepChain<T, P, NF, BT, THREADS, -1> {
+  static __device__ __forceinline__ void run(T*, const T*, int) {}
+};
+template <typename T, int P, int NF, int BT, int THREADS>
+struct StepChain<T, P, NF, BT, THREADS, -2> {
   static __device__ __forceinline__ void run(T*, const T*, int) {}
 };
 
