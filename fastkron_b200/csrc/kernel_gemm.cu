@@ -52,7 +52,7 @@ static bool encodeInputMap(CUtensorMap* tm, const void* X, unsigned long long ch
 
 bool gemmSupported(DType dt, uint32_t P, uint32_t Q, uint64_t B) { return gemmEligible(dt, P, Q, B); }
 
-template <typename T, int P, int Q, int TJ, int PC, int STAGES, int MQ, int MJ, bool XT, int UNR, int MINB>
+template <typename T, int P, int Q, int TJ, int PC, int STAGES, int MQ, int MJ, bool XT, int UNR, int MINB, bool PACK = false>
 static fastKronError launchGemmOne(const Pass& ps, const LaunchCtx& cx, int mode) {
   using C = GemmCfg<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT>;
   GemmArgs<T> a;
@@ -72,7 +72,7 @@ static fastKronError launchGemmOne(const Pass& ps, const LaunchCtx& cx, int mode
   if (a.numTiles == 0) return fastKronSuccess;
   if (a.numTiles >= (1ull << 31) / C::NCH) return fastKronKernelNotFound;   // 32-bit tile counters
 
-  auto kern = gemmPassKernel<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT, UNR, MINB>;
+  auto kern = gemmPassKernel<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT, UNR, MINB, PACK>;
   static int ctasPerSm = 0;
   if (ctasPerSm == 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
@@ -98,10 +98,12 @@ static fastKronError launchGemmOne(const Pass& ps, const LaunchCtx& cx, int mode
   return cudaToFk(cudaGetLastError());
 }
 
-// Tile shapes per factor size.  They come from a sweep on B200 (variants that spill
-// or hold fewer than two CTAs per SM lose 10-15%): fp32 64x64 runs 128-thread CTAs,
-// three per SM; fp32 128x128 keeps the 64 KB factor resident and gives each thread a
-// 16x8 block so that two CTAs still fit.
+// Tile shapes per factor size, from a sweep on B200.  fp32 64x64 runs 128-thread CTAs, three
+// per SM (variants that spill or hold fewer CTAs lose 10-15%).  The packed-FMA inner loop
+// (fma.rn.f32x2) wins where the scalar loop was short of issue slots: the contiguous-
+// contraction layout (+4%) and 128x128, where it makes an 8x16 block per thread on a
+// 256-wide tile the best shape (+8%); the plain 64x64 pass measured the same either way
+// and stays scalar.
 fastKronError launchGemm(const Pass& ps, const LaunchCtx& cx) {
   if (ps.nf != 1 || ps.xsB != 1 || ps.zsB != 1) return fastKronKernelNotFound;
   const uint32_t P = ps.P[0], Q = ps.Q[0];
@@ -113,11 +115,14 @@ fastKronError launchGemm(const Pass& ps, const LaunchCtx& cx) {
     constexpr int TJ = 128;
     const int mode = xt ? 2 : (ps.B % TJ == 0 ? 0 : 1);
     if (P == 64 && Q == 64) {
-      if (xt) return launchGemmOne<float, 64, 64, TJ, 32, 3, 8, 8, true, 8, 3>(ps, cx, mode);
+      if (xt) return launchGemmOne<float, 64, 64, TJ, 32, 3, 8, 8, true, 8, 3, true>(ps, cx, mode);
       return launchGemmOne<float, 64, 64, TJ, 32, 3, 8, 8, false, 16, 3>(ps, cx, mode);
     }
     if (P == 128 && Q == 128) {
-      if (xt) return launchGemmOne<float, 128, 128, TJ, 32, 2, 8, 8, true, 8, 1>(ps, cx, mode);
+      if (xt) return launchGemmOne<float, 128, 128, TJ, 32, 2, 8, 8, true, 8, 1, true>(ps, cx, mode);
+      constexpr int TW = 256;                       // wide tile where the trailing extent allows it
+      if (ps.B % TW == 0 || TW % ps.B == 0)
+        return launchGemmOne<float, 128, 128, TW, 32, 3, 8, 16, false, 8, 1, true>(ps, cx, ps.B % TW == 0 ? 0 : 1);
       return launchGemmOne<float, 128, 128, TJ, 16, 3, 16, 8, false, 8, 2>(ps, cx, mode);
     }
   } else {

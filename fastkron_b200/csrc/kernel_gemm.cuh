@@ -115,7 +115,75 @@ struct GemmCfg {
   static_assert(MQ % VEC == 0 && MJ % VEC == 0 && PC % VEC == 0, "vector shape");
 };
 
-template <typename T, int P, int Q, int TJ, int PC, int STAGES, int MQ, int MJ, bool XT, int UNR = 8, int MINB = 0>
+// The MQ x MJ accumulators of one thread.  With PACK, fp32 blocks are held as pairs and updated with the
+// packed instruction of sm_100 (fma.rn.f32x2: two independent IEEE fp32 FMAs per lane, hence
+// bit-identical to two scalar FMAs, for one issue slot); the scalar FFMA stream of this loop
+// needs every issue slot of the SM for the arithmetic alone, so each shared-memory load,
+// address update or barrier costs FMA throughput, and the packed form frees half of the
+// slots.  Pairs run along j (the operand pair comes straight out of the 128-bit X load and
+// the factor value is duplicated into both halves), or along q in the layout whose X values
+// arrive one p-vector per j (the factor pair is natural there and x is duplicated).
+template <typename T, int MQ, int MJ, bool PAIRQ, bool PACK>
+struct AccBlock {
+  T v[MQ][MJ];
+  __device__ __forceinline__ T& at(int q, int j) { return v[q][j]; }
+  __device__ __forceinline__ void clear() {
+#pragma unroll
+    for (int i = 0; i < MQ; i++)
+#pragma unroll
+      for (int j = 0; j < MJ; j++) v[i][j] = T(0);
+  }
+  // v[q][j] += f[q] * x[j] for the whole block
+  __device__ __forceinline__ void rank1(const T (&f)[MQ], const T (&x)[MJ]) {
+#pragma unroll
+    for (int i = 0; i < MQ; i++)
+#pragma unroll
+      for (int j = 0; j < MJ; j++) v[i][j] = fma(f[i], x[j], v[i][j]);
+  }
+};
+
+template <int MQ, int MJ>
+struct AccBlock<float, MQ, MJ, false, true> {
+  static_assert(MJ % 2 == 0, "pairs along j");
+  float2 v[MQ][MJ / 2];
+  __device__ __forceinline__ float& at(int q, int j) { return (j & 1) ? v[q][j >> 1].y : v[q][j >> 1].x; }
+  __device__ __forceinline__ void clear() {
+#pragma unroll
+    for (int i = 0; i < MQ; i++)
+#pragma unroll
+      for (int j = 0; j < MJ / 2; j++) v[i][j] = make_float2(0.f, 0.f);
+  }
+  __device__ __forceinline__ void rank1(const float (&f)[MQ], const float (&x)[MJ]) {
+#pragma unroll
+    for (int i = 0; i < MQ; i++) {
+      const float2 ff = make_float2(f[i], f[i]);
+#pragma unroll
+      for (int j = 0; j < MJ / 2; j++) v[i][j] = __ffma2_rn(ff, make_float2(x[2 * j], x[2 * j + 1]), v[i][j]);
+    }
+  }
+};
+template <int MQ, int MJ>
+struct AccBlock<float, MQ, MJ, true, true> {
+  static_assert(MQ % 2 == 0, "pairs along q");
+  float2 v[MQ / 2][MJ];
+  __device__ __forceinline__ float& at(int q, int j) { return (q & 1) ? v[q >> 1][j].y : v[q >> 1][j].x; }
+  __device__ __forceinline__ void clear() {
+#pragma unroll
+    for (int i = 0; i < MQ / 2; i++)
+#pragma unroll
+      for (int j = 0; j < MJ; j++) v[i][j] = make_float2(0.f, 0.f);
+  }
+  __device__ __forceinline__ void rank1(const float (&f)[MQ], const float (&x)[MJ]) {
+#pragma unroll
+    for (int j = 0; j < MJ; j++) {
+      const float2 xx = make_float2(x[j], x[j]);
+#pragma unroll
+      for (int i = 0; i < MQ / 2; i++) v[i][j] = __ffma2_rn(make_float2(f[2 * i], f[2 * i + 1]), xx, v[i][j]);
+    }
+  }
+};
+
+template <typename T, int P, int Q, int TJ, int PC, int STAGES, int MQ, int MJ, bool XT, int UNR = 8, int MINB = 0, bool PACK = false>
 __global__ void __launch_bounds__((Q / MQ) * (TJ / MJ), (MINB > 0 ? MINB : ((Q / MQ) * (TJ / MJ) <= 256 ? 2 : 1)))
 gemmPassKernel(const GemmArgs<T> a, const __grid_constant__ CUtensorMap tmap) {
   using C = GemmCfg<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT>;
@@ -232,11 +300,8 @@ gemmPassKernel(const GemmArgs<T> a, const __grid_constant__ CUtensorMap tmap) {
     if (++isSlot == STAGES) isSlot = 0;
   };
 
-  T acc[MQ][MJ];
-#pragma unroll
-  for (int i = 0; i < MQ; i++)
-#pragma unroll
-    for (int j = 0; j < MJ; j++) acc[i][j] = T(0);
+  AccBlock<T, MQ, MJ, XT, PACK && sizeof(T) == 4> acc;
+  acc.clear();
 
 #pragma unroll
   for (int s = 0; s < STAGES - 1; s++) {
@@ -271,11 +336,12 @@ gemmPassKernel(const GemmArgs<T> a, const __grid_constant__ CUtensorMap tmap) {
         for (int g = 0; g < NGJ; g++) xv[g] = *reinterpret_cast<const V*>(xr + pl * TJ + g * JS);
 #pragma unroll
         for (int g = 0; g < NGQ; g++) fv[g] = *reinterpret_cast<const V*>(fr + pl * Q + g * QS);
+        T fq[MQ], xj[MJ];
 #pragma unroll
-        for (int qi = 0; qi < MQ; qi++)
+        for (int qi = 0; qi < MQ; qi++) fq[qi] = fv[qi / VEC].v[qi % VEC];
 #pragma unroll
-          for (int ji = 0; ji < MJ; ji++)
-            acc[qi][ji] = fma(fv[qi / VEC].v[qi % VEC], xv[ji / VEC].v[ji % VEC], acc[qi][ji]);
+        for (int ji = 0; ji < MJ; ji++) xj[ji] = xv[ji / VEC].v[ji % VEC];
+        acc.rank1(fq, xj);
       }
     } else {
       const T* xr = st + tj * (PC + C::PAD);
@@ -289,11 +355,12 @@ gemmPassKernel(const GemmArgs<T> a, const __grid_constant__ CUtensorMap tmap) {
           V fv[NGQ];
 #pragma unroll
           for (int g = 0; g < NGQ; g++) fv[g] = *reinterpret_cast<const V*>(fr + (p0 + pp) * Q + g * QS);
+          T fq[MQ], xj[MJ];
 #pragma unroll
-          for (int qi = 0; qi < MQ; qi++)
+          for (int qi = 0; qi < MQ; qi++) fq[qi] = fv[qi / VEC].v[qi % VEC];
 #pragma unroll
-            for (int ji = 0; ji < MJ; ji++)
-              acc[qi][ji] = fma(fv[qi / VEC].v[qi % VEC], xv[ji].v[pp], acc[qi][ji]);
+          for (int ji = 0; ji < MJ; ji++) xj[ji] = xv[ji].v[pp];
+          acc.rank1(fq, xj);
         }
       }
     }
@@ -316,7 +383,7 @@ gemmPassKernel(const GemmArgs<T> a, const __grid_constant__ CUtensorMap tmap) {
             for (int g = 0; g < NGJ; g++) {
               V o;
 #pragma unroll
-              for (int e = 0; e < VEC; e++) o.v[e] = acc[qi][g * VEC + e];
+              for (int e = 0; e < VEC; e++) o.v[e] = acc.at(qi, g * VEC + e);
               *reinterpret_cast<V*>(pq + g * JS) = o;
             }
           }
@@ -330,7 +397,7 @@ gemmPassKernel(const GemmArgs<T> a, const __grid_constant__ CUtensorMap tmap) {
               for (int g = 0; g < NGQ; g++) {
                 V o;
 #pragma unroll
-                for (int e = 0; e < VEC; e++) o.v[e] = acc[g * VEC + e][ji];
+                for (int e = 0; e < VEC; e++) o.v[e] = acc.at(g * VEC + e, ji);
                 *reinterpret_cast<V*>(p0 + (size_t)ji * JT * Q + g * QS) = o;
               }
             }
@@ -373,7 +440,7 @@ gemmPassKernel(const GemmArgs<T> a, const __grid_constant__ CUtensorMap tmap) {
               }
               V o;
 #pragma unroll
-              for (int e = 0; e < VEC; e++) o.v[e] = epi ? a.alpha * acc[qi][g * VEC + e] : acc[qi][g * VEC + e];
+              for (int e = 0; e < VEC; e++) o.v[e] = epi ? a.alpha * acc.at(qi, g * VEC + e) : acc.at(qi, g * VEC + e);
               if (useY) {
                 const V y = *reinterpret_cast<const V*>(a.Y + (dst - a.Z));
 #pragma unroll
@@ -395,13 +462,13 @@ gemmPassKernel(const GemmArgs<T> a, const __grid_constant__ CUtensorMap tmap) {
                 // redistributed rows are not contiguous in q: one element at a time
 #pragma unroll
                 for (int e = 0; e < VEC; e++)
-                  *gemmOutRow<T, Q>(a, n, g * QS + tq * VEC + e) = epi ? a.alpha * acc[g * VEC + e][ji] : acc[g * VEC + e][ji];
+                  *gemmOutRow<T, Q>(a, n, g * QS + tq * VEC + e) = epi ? a.alpha * acc.at(g * VEC + e, ji) : acc.at(g * VEC + e, ji);
                 continue;
               }
               const unsigned long long off = n * Q + g * QS + tq * VEC;
               V o;
 #pragma unroll
-              for (int e = 0; e < VEC; e++) o.v[e] = epi ? a.alpha * acc[g * VEC + e][ji] : acc[g * VEC + e][ji];
+              for (int e = 0; e < VEC; e++) o.v[e] = epi ? a.alpha * acc.at(g * VEC + e, ji) : acc.at(g * VEC + e, ji);
               if (useY) {
                 const V y = *reinterpret_cast<const V*>(a.Y + off);
 #pragma unroll
@@ -412,10 +479,7 @@ gemmPassKernel(const GemmArgs<T> a, const __grid_constant__ CUtensorMap tmap) {
           }
         }
       }
-#pragma unroll
-      for (int i = 0; i < MQ; i++)
-#pragma unroll
-        for (int j = 0; j < MJ; j++) acc[i][j] = T(0);
+      acc.clear();
       curTile += step;
     }
     if (++c == C::NCH) c = 0;
