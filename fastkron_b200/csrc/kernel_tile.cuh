@@ -117,6 +117,55 @@ __host__ __device__ __forceinline__ void schedFence() {
 
 // ---- one contraction step over a tile of E elements, mode stride S ----------
 
+// fp32 steps use the packed FMA of sm_100 (fma.rn.f32x2: two independent IEEE fp32 FMAs per
+// lane and instruction, bit-identical to two scalar FMAs) on the device; the host build of
+// these templates (the CPU emulation of the tile kernels) keeps the scalar form.
+#if defined(__CUDA_ARCH__) && !defined(FKB_NO_FFMA2)
+constexpr bool kPackedFma = true;
+#else
+constexpr bool kPackedFma = false;
+#endif
+
+// Accumulators of a strided step: U groups of W neighbouring fibres, P outputs each.
+// axpy(u, q, f, x): acc[u][k][q] += f * x[k] for the W fibres of group u.
+template <typename T, int U, int W, int P, bool PACK>
+struct FibreAcc {
+  T v[U][W][P];
+  __host__ __device__ __forceinline__ void clear() {
+#pragma unroll
+    for (int u = 0; u < U; u++)
+#pragma unroll
+      for (int k = 0; k < W; k++)
+#pragma unroll
+        for (int q = 0; q < P; q++) v[u][k][q] = T(0);
+  }
+  __host__ __device__ __forceinline__ void axpy(int u, int q, T f, const T (&x)[W]) {
+#pragma unroll
+    for (int k = 0; k < W; k++) v[u][k][q] = fma(x[k], f, v[u][k][q]);
+  }
+  __host__ __device__ __forceinline__ T at(int u, int k, int q) const { return v[u][k][q]; }
+};
+#if defined(__CUDA_ARCH__)
+template <int U, int W, int P>
+struct FibreAcc<float, U, W, P, true> {
+  float2 v[U][W / 2][P];
+  __device__ __forceinline__ void clear() {
+#pragma unroll
+    for (int u = 0; u < U; u++)
+#pragma unroll
+      for (int k = 0; k < W / 2; k++)
+#pragma unroll
+        for (int q = 0; q < P; q++) v[u][k][q] = make_float2(0.f, 0.f);
+  }
+  __device__ __forceinline__ void axpy(int u, int q, float f, const float (&x)[W]) {
+    const float2 ff = make_float2(f, f);
+#pragma unroll
+    for (int k = 0; k < W / 2; k++) v[u][k][q] = __ffma2_rn(make_float2(x[2 * k], x[2 * k + 1]), ff, v[u][k][q]);
+  }
+  __device__ __forceinline__ float at(int u, int k, int q) const { return (k & 1) ? v[u][k >> 1][q].y : v[u][k >> 1][q].x; }
+};
+#endif
+
 // Strided fibres, S >= W: a thread owns NFIB = kAcc/P fibres, as U groups of W
 // neighbouring ones (W * sizeof(T) <= 16 bytes); every access is one W-wide
 // shared-memory transaction, consecutive lanes take consecutive groups.
@@ -142,13 +191,8 @@ __host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const
       const unsigned hi = (unsigned)vg / (S / W);
       pb[u] = physIdx<T>(hi * (unsigned)(S * P) + lo * W);
     }
-    T acc[U][W][P];
-#pragma unroll
-    for (int u = 0; u < U; u++)
-#pragma unroll
-      for (int k = 0; k < W; k++)
-#pragma unroll
-        for (int q = 0; q < P; q++) acc[u][k][q] = T(0);
+    FibreAcc<T, U, W, P, kPackedFma && (W % 2 == 0)> acc;
+    acc.clear();
 
     // Partially unrolled on purpose: a fully unrolled step of P = 16 or 32 is several
     // thousand instructions and the fused kernels then miss in the instruction cache.
@@ -172,9 +216,7 @@ __host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const
 #pragma unroll
         for (int u = 0; u < U; u++)
 #pragma unroll
-          for (int k = 0; k < W; k++)
-#pragma unroll
-            for (int i = 0; i < FV; i++) acc[u][k][q0 + i] = fma(xv[u].v[k], f[i], acc[u][k][q0 + i]);
+          for (int i = 0; i < FV; i++) acc.axpy(u, q0 + i, f[i], xv[u].v);
       }
       schedFence();
     }
@@ -184,12 +226,49 @@ __host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const
       for (int u = 0; u < U; u++) {
         V ov;
 #pragma unroll
-        for (int k = 0; k < W; k++) ov.v[k] = acc[u][k][q];
+        for (int k = 0; k < W; k++) ov.v[k] = acc.at(u, k, q);
         if (ok[u]) *reinterpret_cast<V*>(tile + (pb[u] ^ physIdx<T>((unsigned)(q * S)))) = ov;
       }
     }
   }
 }
+
+// Accumulators of a contiguous step: NFIB whole fibres of P outputs.
+// axpy(k, q0, x, f): acc[k][q0 + i] += x * f[i] for one 16-byte piece f of a factor row.
+template <typename T, int NFIB, int P, bool PACK>
+struct RowAcc {
+  static constexpr int VEC = Vec16<T>::N;
+  T v[NFIB][P];
+  __host__ __device__ __forceinline__ void clear() {
+#pragma unroll
+    for (int k = 0; k < NFIB; k++)
+#pragma unroll
+      for (int q = 0; q < P; q++) v[k][q] = T(0);
+  }
+  __host__ __device__ __forceinline__ void axpy(int k, int q0, T x, const T (&f)[VEC]) {
+#pragma unroll
+    for (int i = 0; i < VEC; i++) v[k][q0 + i] = fma(x, f[i], v[k][q0 + i]);
+  }
+  __host__ __device__ __forceinline__ T at(int k, int q) const { return v[k][q]; }
+};
+#if defined(__CUDA_ARCH__)
+template <int NFIB, int P>
+struct RowAcc<float, NFIB, P, true> {
+  float2 v[NFIB][P / 2];
+  __device__ __forceinline__ void clear() {
+#pragma unroll
+    for (int k = 0; k < NFIB; k++)
+#pragma unroll
+      for (int q = 0; q < P / 2; q++) v[k][q] = make_float2(0.f, 0.f);
+  }
+  __device__ __forceinline__ void axpy(int k, int q0, float x, const float (&f)[4]) {
+    const float2 xx = make_float2(x, x);
+    v[k][q0 / 2] = __ffma2_rn(xx, make_float2(f[0], f[1]), v[k][q0 / 2]);
+    v[k][q0 / 2 + 1] = __ffma2_rn(xx, make_float2(f[2], f[3]), v[k][q0 / 2 + 1]);
+  }
+  __device__ __forceinline__ float at(int k, int q) const { return (q & 1) ? v[k][q >> 1].y : v[k][q >> 1].x; }
+};
+#endif
 
 // Contiguous fibres (S == 1, P >= VEC): a thread owns NFIB whole fibres, reads
 // and writes them as 128-bit pieces along p / q.
@@ -209,11 +288,8 @@ __host__ __device__ __forceinline__ void stepContig(T* __restrict__ tile, const 
       if (!ok[k]) f = f0;
       pb[k] = physIdx<T>((unsigned)f * P);
     }
-    T acc[NFIB][P];
-#pragma unroll
-    for (int k = 0; k < NFIB; k++)
-#pragma unroll
-      for (int q = 0; q < P; q++) acc[k][q] = T(0);
+    RowAcc<T, NFIB, P, kPackedFma> acc;
+    acc.clear();
 
 #pragma unroll((P / VEC) < (kStepUnroll / VEC) ? (P / VEC) : (kStepUnroll / VEC > 0 ? kStepUnroll / VEC : 1))
     for (int p0 = 0; p0 < P; p0 += VEC) {
@@ -227,9 +303,7 @@ __host__ __device__ __forceinline__ void stepContig(T* __restrict__ tile, const 
         for (int q0 = 0; q0 < P; q0 += VEC) {
           const V fv = *reinterpret_cast<const V*>(Fs + (p0 + pp) * P + q0);
 #pragma unroll
-          for (int k = 0; k < NFIB; k++)
-#pragma unroll
-            for (int i = 0; i < VEC; i++) acc[k][q0 + i] = fma(xv[k].v[pp], fv.v[i], acc[k][q0 + i]);
+          for (int k = 0; k < NFIB; k++) acc.axpy(k, q0, xv[k].v[pp], fv.v);
         }
         schedFence();
       }
@@ -240,7 +314,7 @@ __host__ __device__ __forceinline__ void stepContig(T* __restrict__ tile, const 
       for (int k = 0; k < NFIB; k++) {
         V ov;
 #pragma unroll
-        for (int i = 0; i < VEC; i++) ov.v[i] = acc[k][q0 + i];
+        for (int i = 0; i < VEC; i++) ov.v[i] = acc.at(k, q0 + i);
         if (ok[k]) *reinterpret_cast<V*>(tile + (pb[k] ^ physIdx<T>((unsigned)q0))) = ov;
       }
     }

@@ -19,6 +19,7 @@ using namespace fkb;
 template <typename T, int P, int Q, int TJ, int PC, int STAGES, int MQ, int MJ, bool XT, int UNR, int MINB, bool PACK>
 static void runVariant(const char* name, const T* X, T* Z, const T* F, unsigned long long chunks, unsigned long long B) {
   using C = GemmCfg<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT>;
+  if (const char* flt = getenv("FKB_TUNE_FILTER")) if (!strstr(name, flt)) return;
   GemmArgs<T> a{};
   a.X = X; a.Z = Z; a.Y = nullptr; a.F = F; a.fsP = Q; a.fsQ = 1; a.numChunks = chunks; a.B = B;
   a.alpha = 1; a.beta = 0; a.epilogue = 0;
@@ -237,6 +238,10 @@ int main() {
   RUN(64, 64, 128, 32, 3, 8, 8, false, 8, 3, ch, Bb);
   RUN(64, 64, 128, 32, 3, 8, 8, false, 4, 3, ch, Bb);
   RUN(64, 64, 128, 32, 4, 8, 8, false, 8, 3, ch, Bb);
+  RUN(64, 64, 128, 32, 2, 8, 8, false, 16, 4, ch, Bb);
+  RUN(64, 64, 128, 16, 3, 8, 8, false, 16, 4, ch, Bb);
+  RUN(64, 64, 128, 16, 4, 8, 8, false, 16, 4, ch, Bb);
+  RUN(64, 64, 128, 32, 3, 8, 8, false, 32, 3, ch, Bb);
   RUN(64, 64, 128, 16, 4, 8, 8, false, 16, 3, ch, Bb);
   RUN(64, 64, 128, 64, 2, 8, 8, false, 8, 3, ch, Bb);
   RUN(64, 64, 256, 32, 3, 8, 8, false, 8, 2, ch, Bb);
