@@ -127,8 +127,12 @@ constexpr bool kPackedFma = false;
 #endif
 
 // Accumulators of a strided step: U groups of W neighbouring fibres, P outputs each.
-// axpy(u, q, f, x): acc[u][k][q] += f * x[k] for the W fibres of group u.
-template <typename T, int U, int W, int P, bool PACK>
+// axpy(u, q0, f, x): acc[u][k][q0 + i] += f[i] * x[k] for the W fibres of group u and one
+// piece f[0..FV) of a factor row.  MODE 0: scalar FMAs.  MODE 1: pairs of neighbouring
+// fibres (the x pair is natural, f is duplicated into both halves: FV moves per piece).
+// MODE 2: pairs of neighbouring q (the f pair is natural, x is duplicated: W moves per
+// piece); the cheaper of the two is chosen from the shape.
+template <typename T, int U, int W, int P, int FV, int MODE>
 struct FibreAcc {
   T v[U][W][P];
   __host__ __device__ __forceinline__ void clear() {
@@ -139,15 +143,17 @@ struct FibreAcc {
 #pragma unroll
         for (int q = 0; q < P; q++) v[u][k][q] = T(0);
   }
-  __host__ __device__ __forceinline__ void axpy(int u, int q, T f, const T (&x)[W]) {
+  __host__ __device__ __forceinline__ void axpy(int u, int q0, const T (&f)[FV], const T (&x)[W]) {
 #pragma unroll
-    for (int k = 0; k < W; k++) v[u][k][q] = fma(x[k], f, v[u][k][q]);
+    for (int k = 0; k < W; k++)
+#pragma unroll
+      for (int i = 0; i < FV; i++) v[u][k][q0 + i] = fma(x[k], f[i], v[u][k][q0 + i]);
   }
   __host__ __device__ __forceinline__ T at(int u, int k, int q) const { return v[u][k][q]; }
 };
 #if defined(__CUDA_ARCH__)
-template <int U, int W, int P>
-struct FibreAcc<float, U, W, P, true> {
+template <int U, int W, int P, int FV>
+struct FibreAcc<float, U, W, P, FV, 1> {
   float2 v[U][W / 2][P];
   __device__ __forceinline__ void clear() {
 #pragma unroll
@@ -157,12 +163,38 @@ struct FibreAcc<float, U, W, P, true> {
 #pragma unroll
         for (int q = 0; q < P; q++) v[u][k][q] = make_float2(0.f, 0.f);
   }
-  __device__ __forceinline__ void axpy(int u, int q, float f, const float (&x)[W]) {
-    const float2 ff = make_float2(f, f);
+  __device__ __forceinline__ void axpy(int u, int q0, const float (&f)[FV], const float (&x)[W]) {
 #pragma unroll
-    for (int k = 0; k < W / 2; k++) v[u][k][q] = __ffma2_rn(make_float2(x[2 * k], x[2 * k + 1]), ff, v[u][k][q]);
+    for (int i = 0; i < FV; i++) {
+      const float2 ff = make_float2(f[i], f[i]);
+#pragma unroll
+      for (int k = 0; k < W / 2; k++)
+        v[u][k][q0 + i] = __ffma2_rn(make_float2(x[2 * k], x[2 * k + 1]), ff, v[u][k][q0 + i]);
+    }
   }
   __device__ __forceinline__ float at(int u, int k, int q) const { return (k & 1) ? v[u][k >> 1][q].y : v[u][k >> 1][q].x; }
+};
+template <int U, int W, int P, int FV>
+struct FibreAcc<float, U, W, P, FV, 2> {
+  float2 v[U][W][P / 2];
+  __device__ __forceinline__ void clear() {
+#pragma unroll
+    for (int u = 0; u < U; u++)
+#pragma unroll
+      for (int k = 0; k < W; k++)
+#pragma unroll
+        for (int q = 0; q < P / 2; q++) v[u][k][q] = make_float2(0.f, 0.f);
+  }
+  __device__ __forceinline__ void axpy(int u, int q0, const float (&f)[FV], const float (&x)[W]) {
+#pragma unroll
+    for (int k = 0; k < W; k++) {
+      const float2 xx = make_float2(x[k], x[k]);
+#pragma unroll
+      for (int i = 0; i < FV / 2; i++)
+        v[u][k][q0 / 2 + i] = __ffma2_rn(xx, make_float2(f[2 * i], f[2 * i + 1]), v[u][k][q0 / 2 + i]);
+    }
+  }
+  __device__ __forceinline__ float at(int u, int k, int q) const { return (q & 1) ? v[u][k][q >> 1].y : v[u][k][q >> 1].x; }
 };
 #endif
 
@@ -191,7 +223,10 @@ __host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const
       const unsigned hi = (unsigned)vg / (S / W);
       pb[u] = physIdx<T>(hi * (unsigned)(S * P) + lo * W);
     }
-    FibreAcc<T, U, W, P, kPackedFma && (W % 2 == 0)> acc;
+    constexpr int ACC_MODE = !(kPackedFma && sizeof(T) == 4) ? 0
+                             : (FV % 2 == 0 && U * W < P)    ? 2
+                             : (W % 2 == 0)                  ? 1 : 0;
+    FibreAcc<T, U, W, P, FV, ACC_MODE> acc;
     acc.clear();
 
     // Partially unrolled on purpose: a fully unrolled step of P = 16 or 32 is several
@@ -214,9 +249,7 @@ __host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const
           for (int i = 0; i < FV; i++) f[i] = Fs[p * P + q0 + i];
         }
 #pragma unroll
-        for (int u = 0; u < U; u++)
-#pragma unroll
-          for (int i = 0; i < FV; i++) acc.axpy(u, q0 + i, f[i], xv[u].v);
+        for (int u = 0; u < U; u++) acc.axpy(u, q0, f, xv[u].v);
       }
       schedFence();
     }
@@ -514,6 +547,43 @@ __device__ __forceinline__ void forEachTileVector(const unsigned long long* base
   }
 }
 
+// The same enumeration by counter: the i-th vector of this thread (i < tileVectorCount),
+// for loops that want several vectors in flight at once.
+template <typename T, bool WIDE, int SUB, int THREADS>
+__device__ __forceinline__ int tileVectorCount(int nsub) {
+  constexpr int VPS = SUB / Vec16<T>::N;
+  if constexpr (!WIDE) {
+    const int nvec = nsub * VPS;
+    return nvec > (int)threadIdx.x ? (nvec - (int)threadIdx.x + THREADS - 1) / THREADS : 0;
+  } else if constexpr (VPS >= THREADS) {
+    return nsub * (VPS / THREADS);
+  } else {
+    constexpr int SPT = THREADS / VPS;
+    const int r0 = threadIdx.x / VPS;
+    return nsub > r0 ? (nsub - r0 + SPT - 1) / SPT : 0;
+  }
+}
+template <typename T, bool WIDE, int SUB, int BT, int THREADS>
+__device__ __forceinline__ void tileVectorAt(const unsigned long long* bases, unsigned long long contigBase,
+                                             unsigned long long B, int i, unsigned& idx, unsigned long long& goff) {
+  constexpr int VEC = Vec16<T>::N;
+  constexpr int VPS = SUB / VEC;
+  if constexpr (!WIDE) {
+    const unsigned v = threadIdx.x + (unsigned)i * THREADS;
+    idx = v * VEC; goff = contigBase + (unsigned long long)v * VEC;
+  } else if constexpr (VPS >= THREADS) {
+    constexpr int PER = VPS / THREADS;
+    const unsigned r = (unsigned)i / PER, j = threadIdx.x + ((unsigned)i % PER) * THREADS;
+    const unsigned w = j * VEC;
+    idx = r * SUB + w; goff = bases[r] + (unsigned long long)(w / BT) * B + (w % BT);
+  } else {
+    constexpr int SPT = THREADS / VPS;
+    const unsigned r = threadIdx.x / VPS + (unsigned)i * SPT;
+    const unsigned w = (threadIdx.x % VPS) * VEC;
+    idx = r * SUB + w; goff = bases[r] + (unsigned long long)(w / BT) * B + (w % BT);
+  }
+}
+
 template <typename T, int P, int NF, bool WIDE>
 __global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tilePassKernel(const TileArgs<T> a) {
   constexpr int THREADS = kTileThreads;
@@ -558,6 +628,35 @@ __global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tilePassKernel(c
 
     const bool epi = a.epilogue != 0;
     const bool useY = epi && a.beta != T(0) && a.Y != nullptr;
+    if (useY) {
+      // Y may be Z itself, so the compiler has to keep every read of Y ahead of the next
+      // store and one vector would be in flight per thread; reading a batch of Y first keeps
+      // EB loads in flight (element i of Y is only ever needed for element i of Z).
+      constexpr int EB = sizeof(T) == 8 ? 4 : 8;
+      const int cnt = tileVectorCount<T, WIDE, SUB, THREADS>(nsub);
+      for (int i0 = 0; i0 < cnt; i0 += EB) {
+        V y[EB];
+#pragma unroll
+        for (int e = 0; e < EB; e++) {
+          if (i0 + e < cnt) {
+            unsigned idx; unsigned long long go;
+            tileVectorAt<T, WIDE, SUB, BT, THREADS>(bases, st0 * G, a.B, i0 + e, idx, go);
+            y[e] = *reinterpret_cast<const V*>(a.Y + go);
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < EB; e++) {
+          if (i0 + e < cnt) {
+            unsigned idx; unsigned long long go;         // recomputed: cheaper than keeping EB offsets live
+            tileVectorAt<T, WIDE, SUB, BT, THREADS>(bases, st0 * G, a.B, i0 + e, idx, go);
+            V o = *reinterpret_cast<const V*>(tile + physIdx<T>(idx));
+#pragma unroll
+            for (int i = 0; i < VEC; i++) o.v[i] = fma(a.beta, y[e].v[i], a.alpha * o.v[i]);
+            *reinterpret_cast<V*>(a.Z + go) = o;
+          }
+        }
+      }
+    } else
     forEachTileVector<T, WIDE, SUB, BT, THREADS>(bases, st0 * G, nsub, a.B, [&](unsigned idx, unsigned long long goff) {
       V o = *reinterpret_cast<const V*>(tile + physIdx<T>(idx));
       if (epi) {
