@@ -1,0 +1,127 @@
+"""The reference's own Python package on top of this library.
+
+oracle/build_pyref.sh installs the unmodified reference `pyfastkron` (its .py files and its
+pybind11 shim pyfastkron/pywrapper.cpp compiled as is) with the module FastKronCUDA linked
+against fastkron_b200/libFastKron.so.  A child process then drives that package the way the
+reference's tests/python/test_torch.py:43-152 does: integer-valued operands (sums are exact),
+a torch.kron reference, alpha = 3, beta = 1, broadcast batch dimensions on X, the factors
+and Z, transposed views, fp16 (the package's own fallback) and gradcheck through
+MKM.apply / KMM.apply.  Shapes follow that sweep, except that its one 8^5 fp64 batched case
+(a 69 GB dense Kronecker matrix on the host) runs with four factors.
+Skipped where the build output is absent."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "oracle", "_ref")
+
+CHILD = r"""
+import ctypes, os, sys
+from functools import reduce
+ref = sys.argv[1]
+link = os.path.join(ref, "libFastKronRefX86.so")
+if not os.path.exists(link):
+    os.symlink("libFastKron.so", link)
+sys.path.insert(0, ref)
+import torch
+import pyfastkron.fastkronbase as base
+assert base.fastkronCUDA is not None, "FastKronCUDA did not load"
+from pyfastkron import FastKronCUDA
+assert "sm_100a" in FastKronCUDA.version(), FastKronCUDA.version()   # this repository's library
+import pyfastkron.fastkrontorch as fk
+lib = ctypes.CDLL(os.path.join(os.path.dirname(os.path.dirname(ref)), "fastkron_b200", "libFastKron.so"))
+lib.fkbLaunchCount.restype = ctypes.c_ulonglong
+
+def prod(v):
+    return reduce(lambda a, b: a * b, v, 1)
+
+def kron_all(fs):
+    out = fs[0]
+    for f in fs[1:]:
+        out = torch.kron(out, f)
+    return out
+
+def run(mm, m, n, p, q, dtype, trX, trF, high=5, bx=(), bf=(), bz=None, grad=False):
+    dev = "cuda"
+    ps, qs = [p] * n, [q] * n
+    K, L = prod(ps), prod(qs)
+    if mm == "mkm":
+        xs = [m, K] if not trX else [K, m]
+        fshape = [[p, q] if not trF else [q, p]] * n
+        zs = [m, L]
+    else:
+        xs = [K, m] if not trX else [m, K]
+        fshape = [[q, p] if not trF else [p, q]] * n
+        zs = [L, m]
+    x = torch.randint(0, high, list(bx) + xs, dtype=dtype).to(dev)
+    fs = [torch.randint(0, high, list(bf) + s, dtype=dtype).to(dev) for s in fshape]
+    z = torch.randint(0, high, list(bz if bz is not None else ()) + zs, dtype=dtype).to(dev)
+    if trX:
+        x = x.mT
+    if trF:
+        fs = [f.mT for f in fs]
+    fs = tuple(fs)
+    if grad:
+        x.requires_grad = True
+        for f in fs:
+            f.requires_grad = True
+        torch.autograd.gradcheck((fk.MKM if mm == "mkm" else fk.KMM).apply, (x, *fs), eps=1e-5, atol=1e-4)
+        return
+    with torch.no_grad():
+        y = fk.gemkm(x, fs, 3.0, 1.0, z) if mm == "mkm" else fk.gekmm(fs, x, 3.0, 1.0, z)
+        torch.cuda.synchronize()
+        # reference one batch entry at a time (the dense Kronecker matrix of one entry is up to 4 GB)
+        batch = torch.broadcast_shapes(tuple(x.shape[:-2]), tuple(fs[0].shape[:-2]), tuple(z.shape[:-2]))
+        nb = prod(batch)
+        xb = torch.broadcast_to(x, batch + tuple(x.shape[-2:])).reshape((nb,) + tuple(x.shape[-2:]))
+        zb = torch.broadcast_to(z, batch + tuple(z.shape[-2:])).reshape((nb,) + tuple(z.shape[-2:]))
+        fb = [torch.broadcast_to(f, batch + tuple(f.shape[-2:])).reshape((nb,) + tuple(f.shape[-2:])) for f in fs]
+        assert tuple(y.shape) == batch + tuple(z.shape[-2:]), (y.shape, batch)
+        yb = y.reshape((nb,) + tuple(z.shape[-2:]))
+        for b in range(nb):
+            kr = kron_all([f[b] for f in fb])
+            want = 3.0 * (torch.matmul(xb[b], kr) if mm == "mkm" else torch.matmul(kr, xb[b])) + zb[b]
+            assert torch.isclose(yb[b], want).all().item(), (mm, m, n, p, q, dtype, trX, trF, bx, bf, bz, b)
+            del kr, want
+
+n0 = lib.fkbLaunchCount()
+f32, f64, f16 = torch.float32, torch.float64, torch.float16
+for mm in ("mkm", "kmm"):
+    run(mm, 16, 5, 8, 8, f32, False, False)
+    run(mm, 10, 5, 6, 6, f32, True, False)
+    run(mm, 16, 5, 8, 8, f32, False, False, bx=(2,), bz=(2,))
+    run(mm, 32, 5, 8, 8, f32, False, False, bx=(2, 3), bf=(2, 3))
+    run(mm, 8, 5, 8, 8, f32, False, False, bx=(2, 1), bf=(3,))
+    run(mm, 2, 5, 8, 8, f32, False, False, bx=(2, 1), bf=(2, 4))
+    run(mm, 32, 4, 8, 8, f32, False, False, bx=(3, 3, 1), bf=(3, 1, 4))
+    run(mm, 24, 4, 8, 8, f32, False, False, bx=(2,), bf=(3, 2))
+    run(mm, 16, 4, 8, 8, f32, False, False, bx=(2,), bf=(3, 2), bz=(3, 1))
+    run(mm, 16, 4, 16, 8, f32, True, True, bx=(2,))
+    run(mm, 32, 5, 8, 8, f32, True, True, bx=(2, 1), bf=(3,))
+    run(mm, 13, 5, 8, 8, f32, True, True, bx=(2, 1), bf=(2, 4))
+    run(mm, 19, 3, 8, 32, f32, True, True, bx=(2,), bf=(3, 2))
+    run(mm, 11, 10, 3, 3, f64, False, True)
+    run(mm, 200, 2, 32, 32, f64, True, True)
+    run(mm, 128, 4, 8, 8, f64, True, True, bx=(2, 1), bf=(2, 4))
+    run(mm, 102, 4, 8, 8, f16, False, False, high=2)
+    run(mm, 102, 4, 8, 8, f16, False, False, high=2, bx=(2,))
+    run(mm, 10, 3, 16, 8, f16, True, False, high=2)
+for mm in ("mkm", "kmm"):
+    run(mm, 5, 4, 6, 6, f64, False, True, bx=(1,), bf=(2,), grad=True)
+    run(mm, 5, 4, 4, 6, f64, True, True, bx=(1,), bf=(2,), grad=True)
+n1 = lib.fkbLaunchCount()
+assert n1 > n0, "no kernel of this library was launched"
+print("REBIND-OK launches", n1 - n0)
+"""
+
+
+@pytest.mark.gpu
+def test_reference_python_package_runs_on_this_library():
+    if not os.path.isdir(os.path.join(REF, "pyfastkron")):
+        pytest.skip("oracle/_ref/pyfastkron not built (oracle/build_pyref.sh)")
+    out = subprocess.run([sys.executable, "-c", CHILD, REF], capture_output=True, text=True, timeout=900)
+    assert out.returncode == 0, (out.stdout[-1500:] + "\n" + out.stderr[-3000:])
+    assert "REBIND-OK" in out.stdout
