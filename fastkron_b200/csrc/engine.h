@@ -2,6 +2,8 @@
 // that walks a plan and launches its passes.
 #pragma once
 
+#include <stdlib.h>
+
 #include <cuda_runtime.h>
 
 #include <map>
@@ -57,6 +59,11 @@ class Engine {
   // See LaunchCtx::tilesPerCta.
   void setTilesPerCta(int n) { tilesPerCta_ = n > 0 ? n : 0; }
   int tilesPerCta() const { return tilesPerCta_; }
+  // fastKronOptionsTF32 on the handle, or FASTKRON_TF32=1 in the environment (read once).
+  bool tf32Enabled() const {
+    static const bool env = [] { const char* e = getenv("FASTKRON_TF32"); return e && e[0] == '1'; }();
+    return env || (options_ & fastKronOptionsTF32) != 0;
+  }
 
   // Result / temporary element counts (per batch entry).
   fastKronError sizes(const Problem& pr, size_t* yElems, size_t* tmpElems) const;

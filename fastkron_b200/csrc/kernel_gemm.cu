@@ -111,6 +111,10 @@ fastKronError launchGemm(const Pass& ps, const LaunchCtx& cx) {
   if (((uintptr_t)cx.src | (uintptr_t)cx.dst | (uintptr_t)cx.Y) & 15) return fastKronKernelNotFound;
   if (cx.fsQ == 1 && (((uintptr_t)cx.F[0]) & 15)) return fastKronKernelNotFound;
   const bool xt = ps.B == 1;
+  if (cx.tf32 && cx.dt == DType::F32) {
+    const fastKronError e = launchGemmTf32(ps, cx);
+    if (e != fastKronKernelNotFound) return e;          // shapes it does not take run in fp32 below
+  }
   if (cx.dt == DType::F32) {
     constexpr int TJ = 128;
     const int mode = xt ? 2 : (ps.B % TJ == 0 ? 0 : 1);

@@ -39,6 +39,8 @@ struct LaunchCtx {
   // n tiles per CTA, so that CTAs retire every few tens of microseconds and a small kernel
   // from another stream (a collective used as a barrier) can get onto the GPU in between.
   int tilesPerCta = 0;
+  // Gemm launcher: opt-in TF32 tensor-core kernel for fp32 passes (fastKronOptionsTF32)
+  bool tf32 = false;
 };
 
 // Each returns fastKronKernelNotFound when the pass does not fit the kernel
@@ -47,6 +49,7 @@ struct LaunchCtx {
 fastKronError launchGeneric(const Pass& ps, const LaunchCtx& cx);
 fastKronError launchTile(const Pass& ps, const LaunchCtx& cx);
 fastKronError launchGemm(const Pass& ps, const LaunchCtx& cx);
+fastKronError launchGemmTf32(const Pass& ps, const LaunchCtx& cx);   // only reached through launchGemm
 
 // True when launchTile / launchGemm have an instantiation for the pass; used
 // by the planner's caller to downgrade a pass to Generic up front.

@@ -57,7 +57,12 @@ enum fastKronBackend {
 enum fastKronOptions {
   fastKronOptionsNone      = 1 << 0,
   fastKronOptionsUseFusion = 1 << 1,  /* allow several factors per kernel     */
-  fastKronOptionsTune      = 1 << 2   /* time candidate plans on first use    */
+  fastKronOptionsTune      = 1 << 2,  /* time candidate plans on first use    */
+  /* Not in the reference.  Opt-in: fp32 passes with 64x64 / 128x128 factors run on the TF32
+   * tensor cores (operands read with a 10-bit mantissa, fp32 accumulation); results then
+   * agree with fp32 only to a few 1e-3 of the row maximum.  Also switched on by the
+   * environment variable FASTKRON_TF32=1.  Off by default. */
+  fastKronOptionsTF32      = 1 << 3
 };
 
 /* reference: include/fastkron.h:74-82 */
