@@ -435,6 +435,22 @@ def run_single(args):
                            "hbm_frac_algorithmic": algorithmic_bytes(cc) / sec / 1e9 / peaks.get("hbm_gbs"),
                            "passes": rr["passes"], "launches_per_step": rr["launches"] // max(3, args.steps)}
 
+    # ---- opt-in TF32 tensor-core path on the same workload (reported beside, never the headline) ----
+    tf32 = None
+    if not args.no_extra and c["dt"] == "f32" and c["mm"] == "mkm":
+        h32 = fastkron_b200.FastKron()
+        h32.set_options(2 | 8)                          # fastKronOptionsUseFusion | fastKronOptionsTF32
+        rr = time_config(h32, c, max(3, min(args.steps, 5)), 3, profile=True)
+        del rr["buffers"]
+        torch.cuda.empty_cache()
+        h32.close()
+        sec = rr["ms_per_step"] * 1e-3
+        slow = max(rr["passes"], key=lambda q: q["ms"]) if rr["passes"] else None
+        tf32 = {"gflops": flops / sec / 1e9, "ms_per_step": rr["ms_per_step"], "passes": rr["passes"],
+                "hbm_frac_slowest_pass": (pass_bytes / (slow["ms"] * 1e-3) / 1e9 / peaks.get("hbm_gbs")) if slow else None,
+                "tolerance": "5e-3 of the row maximum (TF32 operands, fp32 accumulation)",
+                "timeouts": int(fk.get().fkbGemmTcTimeouts())}
+
     cpu = None
     if not args.no_cpu:
         cpu = cpu_sample(c, cpu_rows_for(c), reps=2)
@@ -446,7 +462,7 @@ def run_single(args):
         "vs_baseline": None, "dtype": c["dt"], "data": "synthetic", "config": workload_desc(c, 1),
         "value_harness_count": flops_harness(c) / (r["ms_per_step"] * 1e-3) / 1e9,
         "gpu_launches": r["launches"], "passes": passes, "clocks": clocks, "roofline": roof, "e2e": e2e,
-        "cpu_baseline": cpu, "fma_peak_tflops": fma_peak, "configs": extra,
+        "cpu_baseline": cpu, "fma_peak_tflops": fma_peak, "configs": extra, "tf32_optin": tf32,
     }
     print(json.dumps(out))
 

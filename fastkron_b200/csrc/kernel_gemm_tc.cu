@@ -152,6 +152,10 @@ gemmTf32Kernel(const Args a, const __grid_constant__ CUtensorMap tmX) {
   __shared__ __align__(8) unsigned long long fullBar[NS], emptyBar[NS], accFull[2], accEmpty[2];
   __shared__ unsigned tmemBaseSlot;
   __shared__ int abortFlag;
+  // XT epilogue: a thread holds 32 consecutive q of one chunk, but a coalesced store wants 32
+  // consecutive q across the lanes of a warp; each epilogue warp transposes through its own
+  // 32 x 33 scratch.
+  __shared__ float xpose[XT ? 4 : 1][XT ? 32 * 33 : 1];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -279,21 +283,26 @@ gemmTf32Kernel(const Args a, const __grid_constant__ CUtensorMap tmX) {
               if (epi) { v = a.alpha * v; if (useY) v = fmaf(a.beta, a.Y[o], v); }
               a.Z[o] = v;
             }
-          } else {
+          }
+        }
+        if constexpr (XT) {
+          // rows of this warp: chunks n0 .. n0+31, columns c0 .. c0+31
+          float* sc = xpose[quarter];
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              const unsigned long long o = zoff + (unsigned long long)(c0 + i);
-              float4 v = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
-              if (epi) {
-                v.x *= a.alpha; v.y *= a.alpha; v.z *= a.alpha; v.w *= a.alpha;
-                if (useY) {
-                  const float4 y = *reinterpret_cast<const float4*>(a.Y + o);
-                  v.x = fmaf(a.beta, y.x, v.x); v.y = fmaf(a.beta, y.y, v.y); v.z = fmaf(a.beta, y.z, v.z); v.w = fmaf(a.beta, y.w, v.w);
-                }
-              }
-              *reinterpret_cast<float4*>(a.Z + o) = v;
+          for (int i = 0; i < 32; i++) sc[lane * 33 + i] = __uint_as_float(r[i]);
+          __syncwarp();
+          const unsigned long long nBase = (unsigned long long)t * kRows + quarter * 32u;
+#pragma unroll 8
+          for (int rr = 0; rr < 32; rr++) {
+            const unsigned long long nn = nBase + (unsigned)rr;
+            if (nn < a.numChunks) {
+              const unsigned long long o = nn * (unsigned long long)Q + (unsigned)(c0 + lane);
+              float v = sc[rr * 33 + lane];
+              if (epi) { v = a.alpha * v; if (useY) v = fmaf(a.beta, a.Y[o], v); }
+              a.Z[o] = v;
             }
           }
+          __syncwarp();
         }
       }
     }
@@ -350,7 +359,10 @@ static fastKronError launchOne(const Pass& ps, const LaunchCtx& cx) {
     const unsigned ch = B >= 128 ? 1u : (unsigned)(128 / B);          // chunks per tile
     if (B >= 128) { a.tilesPerChunk = (unsigned)(B / 128); tiles = chunks * a.tilesPerChunk; }
     else { a.chunksPerTile = ch; tiles = (chunks + ch - 1) / ch; }
-    // view [chunks][P][B]; one box = one atom: P rows of 32 consecutive j of one chunk
+    // view [chunks][P][B]; one box = one atom: P rows of 32 consecutive j of one chunk.  (Trailing
+    // extents below 32 would need several chunks side by side in one 128-byte row; a TMA box whose
+    // inner extent is below the swizzle span is not packed that way in shared memory, so those
+    // passes stay on the fp32 kernel.)
     const cuuint64_t dims[3] = {B, (cuuint64_t)P, chunks};
     const cuuint64_t strides[2] = {B * 4, (cuuint64_t)P * B * 4};
     const cuuint32_t box[3] = {32, (cuuint32_t)P, 1};
