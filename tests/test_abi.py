@@ -46,6 +46,18 @@ def test_header_compiles_as_cxx_and_c(tmp_path):
                            str(tmp_path / "t.o")])
 
 
+def test_option_bits_keep_reference_values_and_tf32_is_an_extra_bit(tmp_path):
+    """Reference option values (include/fastkron.h:57-61) are ABI; the TF32 opt-in takes the next free bit."""
+    src = tmp_path / "o.cpp"
+    src.write_text('#include "fastkron.h"\n'
+                   'static_assert(fastKronOptionsNone == 1 && fastKronOptionsUseFusion == 2 && fastKronOptionsTune == 4, "reference values");\n'
+                   'static_assert(fastKronOptionsTF32 == 8, "extension bit");\nint main(){return 0;}\n')
+    subprocess.check_call(["g++", "-std=c++17", "-I", os.path.join(ROOT, "include"), "-c", str(src), "-o",
+                           str(tmp_path / "o.o")])
+    Lh = fk.get()
+    assert hasattr(Lh, "fkbGemmTcTimeouts") and hasattr(Lh, "fkbGemmTmaTimeouts")
+
+
 def test_enum_values_and_strings(L):
     assert (fk.OP_N, fk.OP_T) == (1, 2)
     assert fk.BACKEND_CUDA == 8 and fk.BACKEND_X86 == 2
