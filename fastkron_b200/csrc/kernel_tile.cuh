@@ -434,25 +434,66 @@ __device__ __forceinline__ void stepDmma8Pair(double* __restrict__ tile, const d
   constexpr int P = 8;
   constexpr int Sa = Sb * P;
   const int lane = tid & 31, warp = tid >> 5, r = lane >> 2, t = lane & 3;
-  // first product: A[m = qb = r][k = b = t + 4k'] = Fb[b][qb]
-  const double fb0 = Fb[t * P + r], fb1 = Fb[(t + 4) * P + r];
-  // second product: B[k][n = qa = r], k-step 0 <-> a = 2t, k-step 1 <-> a = 2t + 1
-  const double fa0 = Fa[(2 * t) * P + r], fa1 = Fa[(2 * t + 1) * P + r];
-  const int nblocks = E / (P * P);
-  for (int blk = warp; blk < nblocks; blk += THREADS / 32) {
-    const unsigned lo = (unsigned)blk % Sb, hi = (unsigned)blk / Sb;
-    const unsigned pb = physIdx<double>(hi * (unsigned)(Sa * P) + lo);
-    // B[k = b][n = a = r] = X[a = r][b = t + 4k']
-    const double x0 = tile[pb ^ physIdx<double>((unsigned)(r * Sa + t * Sb))];
-    const double x1 = tile[pb ^ physIdx<double>((unsigned)(r * Sa + (t + 4) * Sb))];
-    double c0 = 0.0, c1 = 0.0;            // C1t[qb = r][a = 2t], [a = 2t + 1]
-    dmma884(c0, c1, fb0, x0);
-    dmma884(c0, c1, fb1, x1);
-    double d0 = 0.0, d1 = 0.0;            // C2t[qb = r][qa = 2t], [qa = 2t + 1]
-    dmma884(d0, d1, c0, fa0);
-    dmma884(d0, d1, c1, fa1);
-    tile[pb ^ physIdx<double>((unsigned)((2 * t) * Sa + r * Sb))] = d0;
-    tile[pb ^ physIdx<double>((unsigned)((2 * t + 1) * Sa + r * Sb))] = d1;
+  if constexpr (Sb == 1) {
+    // The two modes are the innermost ones: a warp takes one 8 x 8 block (64 contiguous doubles).
+    // first product: A[m = qb = r][k = b = t + 4k'] = Fb[b][qb]
+    const double fb0 = Fb[t * P + r], fb1 = Fb[(t + 4) * P + r];
+    // second product: B[k][n = qa = r], k-step 0 <-> a = 2t, k-step 1 <-> a = 2t + 1
+    const double fa0 = Fa[(2 * t) * P + r], fa1 = Fa[(2 * t + 1) * P + r];
+    const int nblocks = E / (P * P);
+    for (int blk = warp; blk < nblocks; blk += THREADS / 32) {
+      const unsigned pb = physIdx<double>((unsigned)blk * (unsigned)(Sa * P));
+      // B[k = b][n = a = r] = X[a = r][b = t + 4k']
+      const double x0 = tile[pb ^ physIdx<double>((unsigned)(r * Sa + t))];
+      const double x1 = tile[pb ^ physIdx<double>((unsigned)(r * Sa + (t + 4)))];
+      double c0 = 0.0, c1 = 0.0;            // C1t[qb = r][a = 2t], [a = 2t + 1]
+      dmma884(c0, c1, fb0, x0);
+      dmma884(c0, c1, fb1, x1);
+      double d0 = 0.0, d1 = 0.0;            // C2t[qb = r][qa = 2t], [qa = 2t + 1]
+      dmma884(d0, d1, c0, fa0);
+      dmma884(d0, d1, c1, fa1);
+      // lanes with odd t store their two outputs in the other order: each store instruction then
+      // touches both halves of the 128-byte lines (2 wavefronts instead of 4)
+      const unsigned o0 = (unsigned)(t & 1), o1 = o0 ^ 1u;
+      tile[pb ^ physIdx<double>((unsigned)((2 * t + o0) * Sa + r))] = o0 ? d1 : d0;
+      tile[pb ^ physIdx<double>((unsigned)((2 * t + o1) * Sa + r))] = o1 ? d1 : d0;
+    }
+  } else {
+    // Outer modes (Sb even): a warp takes two neighbouring blocks (lo, lo + 1) at once so that
+    // its 8-byte accesses cover both halves of the 16-byte shared-memory chunks and its stores
+    // are 16-byte vectors; with the first product's k-steps taking b in {0,1,4,5} and {2,3,6,7}
+    // every load is 2 and every store 4 wavefronts, the minimum.
+    //   first product, one per half h of the a index:  C_h[qb][(a', lo)] = sum_b Fb[b][qb] X[4h + a'][b][lo]
+    //     A[m = qb = r][k] = Fb[b(k)][qb];  B[k][n = r] with n = 2a' + lo
+    //   its C fragment (n = 2t, 2t+1 <-> a' = t, lo = 0, 1) is the A operand (k = t <-> a = 4h + t) of
+    //   second product, one per lo:  D_lo[qb][qa] = sum_a C[qb][a][lo] Fa[a][qa],  B[k = t][n = qa = r] = Fa[4h + t][qa]
+    static_assert(Sb % 2 == 0, "block pairs");
+    const int b0 = (t & 1) | ((t & 2) << 1), b1 = b0 + 2;
+    const double fb0 = Fb[b0 * P + r], fb1 = Fb[b1 * P + r];
+    const double fa0 = Fa[t * P + r], fa1 = Fa[(4 + t) * P + r];
+    const unsigned ap = (unsigned)r >> 1, lob = (unsigned)r & 1u;
+    const int npairs = E / (2 * P * P);
+    for (int pr = warp; pr < npairs; pr += THREADS / 32) {
+      const unsigned blk = 2u * (unsigned)pr;
+      const unsigned lo = blk % Sb, hi = blk / Sb;
+      const unsigned pb = physIdx<double>(hi * (unsigned)(Sa * P) + lo);
+      const double x00 = tile[pb ^ physIdx<double>(ap * Sa + (unsigned)b0 * Sb + lob)];
+      const double x01 = tile[pb ^ physIdx<double>(ap * Sa + (unsigned)b1 * Sb + lob)];
+      const double x10 = tile[pb ^ physIdx<double>((4u + ap) * Sa + (unsigned)b0 * Sb + lob)];
+      const double x11 = tile[pb ^ physIdx<double>((4u + ap) * Sa + (unsigned)b1 * Sb + lob)];
+      double c00 = 0.0, c01 = 0.0, c10 = 0.0, c11 = 0.0;      // c[h][lo] = C[qb = r][a = 4h + t][lo]
+      dmma884(c00, c01, fb0, x00);
+      dmma884(c00, c01, fb1, x01);
+      dmma884(c10, c11, fb0, x10);
+      dmma884(c10, c11, fb1, x11);
+      double d00 = 0.0, d01 = 0.0, d10 = 0.0, d11 = 0.0;      // d[lo][o] = D[qb = r][qa = 2t + o][lo]
+      dmma884(d00, d01, c00, fa0);
+      dmma884(d00, d01, c10, fa1);
+      dmma884(d10, d11, c01, fa0);
+      dmma884(d10, d11, c11, fa1);
+      *reinterpret_cast<double2*>(tile + (pb ^ physIdx<double>((unsigned)((2 * t) * Sa + r * Sb)))) = make_double2(d00, d10);
+      *reinterpret_cast<double2*>(tile + (pb ^ physIdx<double>((unsigned)((2 * t + 1) * Sa + r * Sb)))) = make_double2(d01, d11);
+    }
   }
 }
 #endif
