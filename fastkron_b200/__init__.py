@@ -265,9 +265,11 @@ class HostGeMKM:
             _, te1 = self.h.sizes(1, self.ps, self.qs)
             per_row = (2 * self.K + 2 * self.L + 2 * te1) * self.es
             rows_per_slab = max(1, min(self.M, device_budget_bytes // per_row))
-            # at least 8 slabs when possible, so that the un-overlapped first copy-in and
-            # last copy-out are a small part of the call
-            rows_per_slab = max(1, min(rows_per_slab, -(-self.M // 8)))
+            # about 32 slabs when possible, so that the un-overlapped first copy-in and last
+            # copy-out are a small part of the call, but no slab below 256 MB of input (copy
+            # and launch overheads stay negligible)
+            floor_rows = -(-(256 << 20) // (self.K * self.es))
+            rows_per_slab = max(1, min(rows_per_slab, max(-(-self.M // 32), floor_rows)))
         self.rows = int(rows_per_slab)
         _, te = self.h.sizes(self.rows, self.ps, self.qs)
         dev = "cuda"
