@@ -337,7 +337,18 @@ def run_single(args):
     # ---- roofline of the dominant kernel ------------------------------------------
     fma_peak = measure_fma_peak(c["dt"])
     passes = r["passes"] or []
-    dom = max(passes, key=lambda p: p["ms"]) if passes else None
+    # the dominant kernel = the kernel family with the largest share of the step; its launch
+    # duration = the average over its launches in a step (per-pass times are CUDA events
+    # recorded by the engine around each launch, averaged over the timed steps)
+    dom = None
+    if passes:
+        share = {}
+        for q in passes:
+            share[q["kind"]] = share.get(q["kind"], 0.0) + q["ms"]
+        kind = max(share, key=share.get)
+        idxs = [i for i, q in enumerate(passes) if q["kind"] == kind]
+        dom = {"kind": kind, "ms": share[kind] / len(idxs), "indices": idxs,
+               "ms_min": min(passes[i]["ms"] for i in idxs), "ms_max": max(passes[i]["ms"] for i in idxs)}
     es = 4 if c["dt"] == "f32" else 8
     K = int(np.prod(c["ps"], dtype=object))
     pass_bytes = 2 * c["M"] * K * es                     # one pass reads and writes the matrix once
@@ -345,7 +356,6 @@ def run_single(args):
     if dom is not None:
         # per-launch work of a pass: every pass of these configs moves the whole matrix
         # once; its flops are the call's flops split in proportion to the factors it applies
-        idx = passes.index(dom)
         n_launch = len(passes)
         dom_flops = flops / n_launch if len(set(c["ps"])) == 1 else None
         hbm_ach = pass_bytes / (dom["ms"] * 1e-3) / 1e9
@@ -353,16 +363,16 @@ def run_single(args):
         # scaled by matrix size): reads equal the algorithmic bytes exactly, writes too except for the
         # ~50 MB still dirty in L2 when the kernel ends, i.e. traffic = algorithmic bytes, no re-reads.
         traffic = float(pass_bytes)
-        roof_hbm = {"bound": "hbm", "achieved": hbm_ach, "peak": peaks.get("hbm_gbs"), "unit": "GB/s",
-                    "frac": hbm_ach / peaks.get("hbm_gbs"), "traffic": traffic, "peak_source": peak_src,
-                    "kernel": dom["kind"], "pass_index": idx, "launch_ms": dom["ms"]}
+        common = {"kernel": dom["kind"], "pass_indices": dom["indices"], "launch_ms": dom["ms"],
+                  "launch_ms_min": dom["ms_min"], "launch_ms_max": dom["ms_max"], "launches_per_step": len(dom["indices"])}
+        roof_hbm = dict({"bound": "hbm", "achieved": hbm_ach, "peak": peaks.get("hbm_gbs"), "unit": "GB/s",
+                         "frac": hbm_ach / peaks.get("hbm_gbs"), "traffic": traffic, "peak_source": peak_src}, **common)
         roof = roof_hbm
         if dom_flops is not None and fma_peak > 0:
             fp_ach = dom_flops / (dom["ms"] * 1e-3) / 1e12
-            roof_fp = {"bound": "fp32_simt" if c["dt"] == "f32" else "fp64_simt", "achieved": fp_ach, "peak": fma_peak,
-                       "unit": "TFLOP/s", "frac": fp_ach / fma_peak, "traffic": traffic,
-                       "peak_source": "FMA-chain probe in this run", "kernel": dom["kind"], "pass_index": idx,
-                       "launch_ms": dom["ms"]}
+            roof_fp = dict({"bound": "fp32_simt" if c["dt"] == "f32" else "fp64_simt", "achieved": fp_ach, "peak": fma_peak,
+                            "unit": "TFLOP/s", "frac": fp_ach / fma_peak, "traffic": traffic,
+                            "peak_source": "FMA-chain probe in this run"}, **common)
             if roof_fp["frac"] > roof_hbm["frac"]:
                 roof = dict(roof_fp, other=roof_hbm)
             else:
