@@ -88,7 +88,9 @@ def run(args, CONFIGS, B):
     hz = torch.empty(M * Ll, dtype=torch.float32, pin_memory=True)
     hx.copy_(x)
     torch.cuda.synchronize()
-    nc = 16 if M % 16 == 0 else (8 if M % 8 == 0 else 1)
+    nc = int(os.environ.get("FASTKRON_E2E_CHUNKS", "16"))
+    while nc > 1 and M % nc != 0:
+        nc //= 2
     Mc = M // nc
     # the chunk engine stores straight into the peers from its kernels (the transfers of a chunk
     # are small next to its PCIe copies, so the copy-engine transport of the timed loop above
