@@ -238,56 +238,74 @@ def read_measured_peaks():
         return {"hbm_gbs": 6650.0}, "fallback"
 
 
-def cpu_sample(c, rows, reps, threads=None):
-    """Time the reference x86 backend (oracle/_ref) -- or, where that library is absent,
-    the C restatement -- on `rows` rows of configuration c with all host threads."""
+def cpu_slab_rows(c):
+    """Rows per reference call: the whole configuration when its matrices stay below 2^31
+    elements, otherwise the largest power-of-two row slab that does (at most 128 rows; the
+    reference counts elements in 32 bits, src/kmm/matrix.h:112).  Rows of an MKM are
+    independent, so a call is the sum of its slabs."""
+    K = int(np.prod(c["ps"], dtype=object))
+    L = int(np.prod(c["qs"], dtype=object))
+    width = max(K, L)
+    if c["M"] * width < (1 << 31):
+        return c["M"]
+    rows = 128
+    while rows > 1 and rows * width >= (1 << 31):
+        rows //= 2
+    return rows
+
+
+def cpu_whole(c, reps, warm=1, threads=None):
+    """Time the reference x86 backend (oracle/_ref) -- or, where that library is absent, the
+    C restatement -- on the WHOLE configuration with all host threads.  A configuration too
+    large for one reference call runs as row slabs with their true seeded rows; a step is the
+    sum of its slab times.  Returns per-step seconds (list) and a description."""
     import oracle
     from fastkron_b200 import synth
     ndt = np.float32 if c["dt"] == "f32" else np.float64
     K = int(np.prod(c["ps"], dtype=object))
     L = int(np.prod(c["qs"], dtype=object))
+    M = c["M"]
+    rows = cpu_slab_rows(c)
+    if rows < M and (c["mm"] != "mkm" or c["opx"] != "N" or c["beta"] != 0):
+        raise SystemExit("row slabs are implemented for row-major MKM without Y")
     gen = synth.normal if c["dist"] == "normal" else synth.uniform
-    x = gen(c["seed"], rows * K, ndt)
-    y = gen(c["seed"] + 1000, rows * L, ndt) if c["beta"] != 0 else None
     fs = [synth.uniform(c["seed"] + 2000 + i, p * q, ndt) for i, (p, q) in enumerate(zip(c["ps"], c["qs"]))]
     cores = threads or os.cpu_count() or 1
-    best = None
-    if oracle.ref_available():
-        kind = "reference"
-        ref = oracle.RefLib(threads=cores)
-        z = np.zeros(rows * L, dtype=ndt)
-        _, te = ref.sizes(rows, c["ps"], c["qs"])
-        temps = (np.zeros(te, dtype=ndt), np.zeros(te, dtype=ndt))
-        for i in range(reps + 1):
-            t0 = time.perf_counter()
-            ref.gekmm(c["mm"], x, fs, c["ps"], c["qs"], rows, c["opx"], c["opf"], c["alpha"], c["beta"], y, z=z, temps=temps)
-            dt = time.perf_counter() - t0
-            if i >= 1:
-                best = dt if best is None else min(best, dt)
-        ref.close()
-    else:
-        kind = "port"
+    nslab = -(-M // rows)
+    step = [0.0] * reps
+    use_ref = oracle.ref_available()
+    kind = "reference" if use_ref else "port"
+    ref = oracle.RefLib(threads=cores) if use_ref else None
+    if not use_ref:
         os.environ.setdefault("OMP_NUM_THREADS", str(cores))
-        for i in range(reps + 1):
+    z = temps = None
+    for sl in range(nslab):
+        r0 = sl * rows
+        r = min(rows, M - r0)
+        x = gen(c["seed"], r * K, ndt, offset=r0 * K)
+        y = gen(c["seed"] + 1000, r * L, ndt, offset=r0 * L) if c["beta"] != 0 else None
+        if use_ref and (z is None or z.size != r * L):
+            z = np.zeros(r * L, dtype=ndt)
+            _, te = ref.sizes(r, c["ps"], c["qs"])
+            temps = (np.zeros(te, dtype=ndt), np.zeros(te, dtype=ndt))
+        for i in range(warm + reps):
             t0 = time.perf_counter()
-            oracle.port_gekmm(c["mm"], x, fs, c["ps"], c["qs"], rows, c["opx"], c["opf"], c["alpha"], c["beta"], y)
+            if use_ref:
+                ref.gekmm(c["mm"], x, fs, c["ps"], c["qs"], r, c["opx"], c["opf"], c["alpha"], c["beta"], y, z=z, temps=temps)
+            else:
+                oracle.port_gekmm(c["mm"], x, fs, c["ps"], c["qs"], r, c["opx"], c["opf"], c["alpha"], c["beta"], y)
             dt = time.perf_counter() - t0
-            if i >= 1:
-                best = dt if best is None else min(best, dt)
-    return {"value": flops_library(c, rows) / best / 1e9, "unit": "GFLOP/s", "cores": cores, "kind": kind,
-            "sample": "%d of %d rows of %s, best of %d after 1 warm-up, %.3f s per call" % (rows, c["M"], c["name"], reps, best),
-            "seconds": best}
-
-
-def cpu_rows_for(c):
-    """Rows of the workload that keep one reference call at a few seconds of CPU work
-    (and under the reference's 32-bit element count, src/kmm/matrix.h:112)."""
-    per_row = flops_library(c, 1)
-    rows = max(1, min(c["M"], int(150e9 // per_row)))     # ~150 GFLOP per call
-    K = int(np.prod(c["ps"], dtype=object))
-    while rows > 1 and rows * K >= (1 << 31):
-        rows //= 2
-    return rows
+            if i >= warm:
+                step[i - warm] += dt
+        del x, y
+    if ref is not None:
+        ref.close()
+    best = min(step)
+    return {"value": flops_library(c) / best / 1e9, "unit": "GFLOP/s", "cores": cores, "kind": kind,
+            "sample": "whole %s (%d rows) as %d slab(s) of %d rows, slab times summed; best of %d steps after %d warm-up "
+                      "call(s) per slab: %.3f s per step (mean %.3f s)" % (c["name"], M, nslab, rows, reps, warm, best,
+                                                                          float(np.mean(step))),
+            "seconds": best, "seconds_mean": float(np.mean(step)), "slabs": nslab, "slab_rows": rows}
 
 
 def run_reference(args):
@@ -295,12 +313,14 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rows = cpu_rows_for(c)
     t0 = time.perf_counter()
-    res = cpu_sample(c, rows, reps=max(args.steps, 1))
+    # a step is the whole configuration; warm-up calls are per slab and capped so that the
+    # run stays within a few minutes on any host
+    res = cpu_whole(c, reps=max(1, min(args.steps, 10)), warm=max(1, min(args.warmup, 2)))
     out = {
         "impl": "reference", "metric": "GeMKM/GeKMM GFLOP/s", "value": res["value"], "unit": "GFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["seconds"] * 1e3,
+        "ms_per_step_mean": res["seconds_mean"] * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": c["dt"], "data": "synthetic",
         "config": workload_desc(c, args.gpus),
         "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
@@ -310,12 +330,173 @@ def run_reference(args):
     print(json.dumps(out))
 
 
+def factor_desc(c):
+    """Factor list with runs of equal shapes folded: 4x(64x64), 2x(128x128),16x16."""
+    out, shapes = [], list(zip(c["ps"], c["qs"]))
+    k = 0
+    while k < len(shapes):
+        n = 1
+        while k + n < len(shapes) and shapes[k + n] == shapes[k]:
+            n += 1
+        one = "%dx%d" % shapes[k]
+        out.append(one if n == 1 else "%dx(%s)" % (n, one))
+        k += n
+    return ",".join(out)
+
+
 def workload_desc(c, gpus):
     return {"workload": "%s: %s %s M=%d factors=%s opX=%s opF=%s alpha=%g beta=%g seed=%d" % (
         c["name"], "sge" if c["dt"] == "f32" else "dge", c["mm"], c["M"],
-        "x".join("%dx%d" % (p, q) for p, q in zip(c["ps"], c["qs"])), c["opx"], c["opf"], c["alpha"], c["beta"], c["seed"]),
+        factor_desc(c), c["opx"], c["opf"], c["alpha"], c["beta"], c["seed"]),
         "gpus": gpus, "sharding": "none" if gpus == 1 else "X columns over %d ranks" % gpus,
         "l2": "operands exceed L2 (no flush needed)" if algorithmic_bytes(c) > 2 * 126e6 else "operands fit L2; not flushed"}
+
+
+# DRAM traffic per launch, measured with ncu (dram__bytes_read.sum, dram__bytes_write.sum) on
+# smaller operands of the same kernels and carried to a full launch: reads scale with the
+# matrix (ratio to the algorithmic bytes read), writes are the algorithmic bytes minus what
+# is still dirty in the 126 MB L2 when the kernel ends (an absolute amount, not a ratio).
+NCU_TRAFFIC = {
+    "gemm": {"read_ratio": 1.0004, "dirty_l2_bytes": 53.0e6,
+             "source": "profiles/gemm_kernel_c4_c5.md, C5m pass 3: 268.6 MB read, 215.4 MB written for 268.4 MB each way"},
+    "tile": {"read_ratio": 1.0004, "dirty_l2_bytes": 47.0e6,
+             "source": "profiles/tile_kernels_c1_c2_c3.md, C4p pass 1: 268.5 MB read, 221.4 MB written for 268.4 MB each way"},
+}
+
+
+def carried_traffic(kind, read_bytes, write_bytes):
+    t = NCU_TRAFFIC.get(kind)
+    if t is None:
+        return None, None
+    return t["read_ratio"] * read_bytes + max(0.0, write_bytes - t["dirty_l2_bytes"]), t["source"]
+
+
+def simt_peak_from_props(dt):
+    """SMs x lanes x 2 x maximum SM clock of device 0 (TFLOP/s), from the device properties."""
+    from fastkron_b200 import synth
+    lib = synth._helper()
+    if lib is None or not hasattr(lib, "fkbSimtPeakFromProps"):
+        return 0.0
+    lib.fkbSimtPeakFromProps.restype = ctypes.c_double
+    return float(lib.fkbSimtPeakFromProps(ctypes.c_int(0), ctypes.c_int(0 if dt == "f32" else 1)))
+
+
+def matrix_views(c, x, z, y):
+    """(M, K) / (M, L) views of the stored operands whatever their storage order."""
+    M, mm = c["M"], c["mm"]
+    K = int(np.prod(c["ps"], dtype=object))
+    L = int(np.prod(c["qs"], dtype=object))
+    x_rowmajor = (mm == "mkm") == (c["opx"] == "N")
+    Xv = x.view(M, K) if x_rowmajor else x.view(K, M).t()
+    Zv = z.view(M, L) if mm == "mkm" else z.view(L, M).t()
+    Yv = None if y is None else (y.view(M, L) if mm == "mkm" else y.view(L, M).t())
+    return Xv, Zv, Yv
+
+
+def parity_rows(c, x, fs, y, z, rows=None):
+    """Rows of the device result against the CPU oracle run on those rows (outside any timed
+    region): max |z - ref| / max |ref row|."""
+    import oracle
+    Xv, Zv, Yv = matrix_views(c, x, z, y)
+    M = c["M"]
+    rows = sorted(set(rows or [0, M - 1]))
+    xr = np.ascontiguousarray(Xv[rows].cpu().numpy())
+    yr = None if Yv is None else np.ascontiguousarray(Yv[rows].cpu().numpy())
+    fh = [f.cpu().numpy() for f in fs]
+    opf = c["opf"] if c["mm"] == "mkm" else ("T" if c["opf"] == "N" else "N")
+    want = oracle.port_gekmm("mkm", xr, fh, c["ps"], c["qs"], len(rows), "N", opf, c["alpha"], c["beta"], yr)
+    got = Zv[rows].cpu().numpy().astype(np.float64)
+    den = np.abs(want).max(axis=1, keepdims=True)
+    return float((np.abs(got - want) / den).max())
+
+
+def time_e2e(h, c, bufs, steps):
+    """The same call with HOST operands: X (and Y) start in pinned host memory, Z ends there;
+    every step pays its copies.  Row-major MKM without Y goes through the public pipelined
+    host-operand call (fastkron_b200.HostGeMKM: row slabs, copies overlapped with the
+    product); everything else is copy in, one C-ABI call, copy out."""
+    import torch
+    import fastkron_b200
+    x, fs, y, z, t1, t2 = bufs
+    es = x.element_size()
+    hx = torch.empty(x.numel(), dtype=x.dtype, pin_memory=True)
+    hz = torch.empty(z.numel(), dtype=z.dtype, pin_memory=True)
+    hy = None
+    hx.copy_(x)
+    if y is not None:
+        hy = torch.empty(y.numel(), dtype=y.dtype, pin_memory=True)
+        hy.copy_(y)
+    torch.cuda.synchronize()
+    tt = []
+    if c["mm"] == "mkm" and c["beta"] == 0 and c["opx"] == "N":
+        op = fastkron_b200.HostGeMKM(c["M"], c["ps"], c["qs"], dtype=x.dtype)
+        mode = "row slabs of %d, copies overlapped with the product" % op.rows
+        for it in range(1 + steps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            op(hx.view(c["M"], -1), fs, hz.view(c["M"], -1), c["alpha"])
+            b.record()
+            torch.cuda.synchronize()
+            if it > 0:
+                tt.append(a.elapsed_time(b))
+        op.close()
+    else:
+        mode = "one copy in, one call, one copy out"
+        for it in range(1 + steps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            x.copy_(hx, non_blocking=True)
+            if hy is not None:
+                y.copy_(hy, non_blocking=True)
+            call(h, c, c["M"], x, fs, z, y, t1, t2)
+            hz.copy_(z, non_blocking=True)
+            b.record()
+            torch.cuda.synchronize()
+            if it > 0:
+                tt.append(a.elapsed_time(b))
+    ms = float(np.mean(tt))
+    n = min(1 << 20, z.numel())
+    same = bool(torch.equal(hz[:n], z[:n].cpu()) and torch.equal(hz[-n:], z[-n:].cpu()))
+    h2d = x.numel() * es + (y.numel() * es if y is not None else 0)
+    return {"value": flops_library(c) / (ms * 1e-3) / 1e9, "unit": "GFLOP/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": z.numel() * es, "ms_per_step": ms, "steps": steps, "how": mode,
+            "matches_device_result": same}
+
+
+def dominant_roofline(c, passes, flops, peaks, peak_src, fma_probe, fma_props):
+    """Roofline entry of the kernel family with the largest share of a step.  Its launch
+    duration is the average over its launches in a step (CUDA events the engine records
+    around each launch on the launching stream).  Per launch: algorithmic bytes = the matrix
+    read once and written once (2*M*K*sizeof(T)); algorithmic flops = 2*M*K*P."""
+    if not passes:
+        return None
+    share = {}
+    for q in passes:
+        share[q["kind"]] = share.get(q["kind"], 0.0) + q["ms"]
+    kind = max(share, key=share.get)
+    idxs = [i for i, q in enumerate(passes) if q["kind"] == kind]
+    ms = share[kind] / len(idxs)
+    es = 4 if c["dt"] == "f32" else 8
+    K = int(np.prod(c["ps"], dtype=object))
+    mat = c["M"] * K * es
+    pass_bytes = 2 * mat
+    hbm_ach = pass_bytes / (ms * 1e-3) / 1e9
+    traffic, tsrc = carried_traffic(kind, mat, mat)
+    common = {"kernel": kind, "pass_indices": idxs, "launch_ms": ms,
+              "launch_ms_min": min(passes[i]["ms"] for i in idxs), "launch_ms_max": max(passes[i]["ms"] for i in idxs),
+              "launches_per_step": len(idxs), "algorithmic_bytes": pass_bytes, "traffic": traffic, "traffic_source": tsrc}
+    roof_hbm = dict({"bound": "hbm", "achieved": hbm_ach, "peak": peaks.get("hbm_gbs"), "unit": "GB/s",
+                     "frac": hbm_ach / peaks.get("hbm_gbs"), "peak_source": peak_src + " copy bandwidth"}, **common)
+    dom_flops = flops / len(passes) if len(set(c["ps"])) == 1 and len(idxs) == len(passes) else None
+    fp_peak = max(fma_probe or 0.0, fma_props or 0.0)
+    if dom_flops is None or fp_peak <= 0:
+        return roof_hbm
+    fp_ach = dom_flops / (ms * 1e-3) / 1e12
+    roof_fp = dict({"bound": "fp32_simt" if c["dt"] == "f32" else "fp64_simt", "achieved": fp_ach, "peak": fp_peak,
+                    "unit": "TFLOP/s", "frac": fp_ach / fp_peak,
+                    "peak_source": "larger of the FMA-chain probe of this run (%.1f) and SMs x lanes x 2 x max SM clock "
+                                   "from the device properties (%.1f)" % (fma_probe or 0.0, fma_props or 0.0)}, **common)
+    return dict(roof_fp, other=roof_hbm) if roof_fp["frac"] > roof_hbm["frac"] else dict(roof_hbm, other=roof_fp)
 
 
 def run_single(args):
@@ -334,97 +515,25 @@ def run_single(args):
     flops = flops_library(c)
     value = flops / (r["ms_per_step"] * 1e-3) / 1e9
 
-    # ---- roofline of the dominant kernel ------------------------------------------
-    fma_peak = measure_fma_peak(c["dt"])
+    fma_probe = measure_fma_peak(c["dt"])
+    fma_props = simt_peak_from_props(c["dt"])
     passes = r["passes"] or []
-    # the dominant kernel = the kernel family with the largest share of the step; its launch
-    # duration = the average over its launches in a step (per-pass times are CUDA events
-    # recorded by the engine around each launch, averaged over the timed steps)
-    dom = None
-    if passes:
-        share = {}
-        for q in passes:
-            share[q["kind"]] = share.get(q["kind"], 0.0) + q["ms"]
-        kind = max(share, key=share.get)
-        idxs = [i for i, q in enumerate(passes) if q["kind"] == kind]
-        dom = {"kind": kind, "ms": share[kind] / len(idxs), "indices": idxs,
-               "ms_min": min(passes[i]["ms"] for i in idxs), "ms_max": max(passes[i]["ms"] for i in idxs)}
-    es = 4 if c["dt"] == "f32" else 8
-    K = int(np.prod(c["ps"], dtype=object))
-    pass_bytes = 2 * c["M"] * K * es                     # one pass reads and writes the matrix once
-    roof = None
-    if dom is not None:
-        # per-launch work of a pass: every pass of these configs moves the whole matrix
-        # once; its flops are the call's flops split in proportion to the factors it applies
-        n_launch = len(passes)
-        dom_flops = flops / n_launch if len(set(c["ps"])) == 1 else None
-        hbm_ach = pass_bytes / (dom["ms"] * 1e-3) / 1e9
-        # DRAM traffic per launch from the ncu captures under profiles/ (taken on smaller operands and
-        # scaled by matrix size): reads equal the algorithmic bytes exactly, writes too except for the
-        # ~50 MB still dirty in L2 when the kernel ends, i.e. traffic = algorithmic bytes, no re-reads.
-        traffic = float(pass_bytes)
-        common = {"kernel": dom["kind"], "pass_indices": dom["indices"], "launch_ms": dom["ms"],
-                  "launch_ms_min": dom["ms_min"], "launch_ms_max": dom["ms_max"], "launches_per_step": len(dom["indices"])}
-        roof_hbm = dict({"bound": "hbm", "achieved": hbm_ach, "peak": peaks.get("hbm_gbs"), "unit": "GB/s",
-                         "frac": hbm_ach / peaks.get("hbm_gbs"), "traffic": traffic, "peak_source": peak_src}, **common)
-        roof = roof_hbm
-        if dom_flops is not None and fma_peak > 0:
-            fp_ach = dom_flops / (dom["ms"] * 1e-3) / 1e12
-            roof_fp = dict({"bound": "fp32_simt" if c["dt"] == "f32" else "fp64_simt", "achieved": fp_ach, "peak": fma_peak,
-                            "unit": "TFLOP/s", "frac": fp_ach / fma_peak, "traffic": traffic,
-                            "peak_source": "FMA-chain probe in this run"}, **common)
-            if roof_fp["frac"] > roof_hbm["frac"]:
-                roof = dict(roof_fp, other=roof_hbm)
-            else:
-                roof = dict(roof_hbm, other=roof_fp)
+    roof = dominant_roofline(c, passes, flops, peaks, peak_src, fma_probe, fma_props)
+
+    # ---- parity of the timed result, outside the timed region -----------------------------
+    x, fs, y, z, t1, t2 = r["buffers"]
+    parity = None
+    if not args.no_cpu:
+        parity = parity_rows(c, x, fs, y, z)
 
     # ---- end to end with host buffers ------------------------------------------------------
-    # X and Z in pinned host memory; every step copies X in and Z out.  MKM rows are
-    # independent, so the public host-operand call (fastkron_b200.HostGeMKM) pipelines row
-    # slabs: copy-in, product (the same C ABI sgemkm/dgemkm) and copy-out overlap.
-    x, fs, y, z, t1, t2 = r["buffers"]
-    e2e = None
+    e2e_steps = max(1, min(args.steps, 3))
     try:
-        hx = torch.empty(x.numel(), dtype=x.dtype, pin_memory=True)
-        hz = torch.empty(z.numel(), dtype=z.dtype, pin_memory=True)
-        hx.copy_(x)
-        torch.cuda.synchronize()
-        e2e_steps = max(1, min(args.steps, 3))
-        tt = []
         if c["mm"] == "mkm" and c["beta"] == 0 and c["opx"] == "N":
-            del t1, t2
-            torch.cuda.empty_cache()
-            op = fastkron_b200.HostGeMKM(c["M"], c["ps"], c["qs"], dtype=x.dtype)
-            mode = "row slabs of %d, copies overlapped with the product" % op.rows
-            for it in range(1 + e2e_steps):
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                op(hx.view(c["M"], -1), fs, hz.view(c["M"], -1), c["alpha"])
-                b.record()
-                torch.cuda.synchronize()
-                if it > 0:
-                    tt.append(a.elapsed_time(b))
-            op.close()
             t1 = t2 = None
-        else:
-            mode = "one copy in, one call, one copy out"
-            for it in range(1 + e2e_steps):
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                x.copy_(hx, non_blocking=True)
-                call(h, c, c["M"], x, fs, z, y, t1, t2)
-                hz.copy_(z, non_blocking=True)
-                b.record()
-                torch.cuda.synchronize()
-                if it > 0:
-                    tt.append(a.elapsed_time(b))
-        e2e_ms = float(np.mean(tt))
-        # the copied-out result must be the device result
-        same = bool(torch.equal(hz[: 1 << 20], z[: 1 << 20].cpu()))
-        e2e = {"value": flops / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "h2d_bytes_per_step": x.numel() * es,
-               "d2h_bytes_per_step": z.numel() * es, "ms_per_step": e2e_ms, "steps": e2e_steps, "how": mode,
-               "matches_device_result": same}
-        del hx, hz
+            r["buffers"] = (x, fs, y, z, None, None)
+            torch.cuda.empty_cache()
+        e2e = time_e2e(h, c, (x, fs, y, z, t1, t2), e2e_steps)
     except RuntimeError as ex:      # pinned allocation failed
         e2e = {"value": None, "unit": "GFLOP/s", "error": str(ex)[:200]}
     del x, fs, y, z, t1, t2, r["buffers"]
@@ -435,15 +544,28 @@ def run_single(args):
     if not args.no_extra and args.config == "C5":
         for name in ("C1", "C2", "C3", "C4"):
             cc = dict(CONFIGS[name], name=name)
-            rr = time_config(h, cc, max(3, args.steps), max(3, args.warmup), profile=True)
-            del rr["buffers"]
-            torch.cuda.empty_cache()
+            st = max(3, args.steps)
+            rr = time_config(h, cc, st, max(3, args.warmup), profile=True)
             fl = flops_library(cc)
             sec = rr["ms_per_step"] * 1e-3
-            extra[name] = {"gflops": fl / sec / 1e9, "gflops_harness_count": flops_harness(cc) / sec / 1e9,
-                           "ms_per_step": rr["ms_per_step"], "algorithmic_gbs": algorithmic_bytes(cc) / sec / 1e9,
-                           "hbm_frac_algorithmic": algorithmic_bytes(cc) / sec / 1e9 / peaks.get("hbm_gbs"),
-                           "passes": rr["passes"], "launches_per_step": rr["launches"] // max(3, args.steps)}
+            bx, bf, by, bz, bt1, bt2 = rr["buffers"]
+            ent = {"gflops": fl / sec / 1e9, "gflops_harness_count": flops_harness(cc) / sec / 1e9,
+                   "ms_per_step": rr["ms_per_step"], "ms_min": rr["ms_min"],
+                   "algorithmic_gbs": algorithmic_bytes(cc) / sec / 1e9,
+                   "hbm_frac_algorithmic": algorithmic_bytes(cc) / sec / 1e9 / peaks.get("hbm_gbs"),
+                   "passes": rr["passes"], "launches_per_step": rr["launches"] // st,
+                   "roofline": dominant_roofline(cc, rr["passes"] or [], fl, peaks, peak_src,
+                                                 fma_probe if cc["dt"] == c["dt"] else measure_fma_peak(cc["dt"]),
+                                                 simt_peak_from_props(cc["dt"]))}
+            if not args.no_cpu:
+                ent["parity_rows_max_rel_err"] = parity_rows(cc, bx, bf, by, bz)
+            try:
+                ent["e2e"] = time_e2e(h, cc, rr["buffers"], 3)
+            except RuntimeError as ex:
+                ent["e2e"] = {"value": None, "unit": "GFLOP/s", "error": str(ex)[:200]}
+            del bx, bf, by, bz, bt1, bt2, rr["buffers"]
+            torch.cuda.empty_cache()
+            extra[name] = ent
 
     # ---- opt-in TF32 tensor-core path on the same workload (reported beside, never the headline) ----
     tf32 = None
@@ -456,6 +578,8 @@ def run_single(args):
         h32.close()
         sec = rr["ms_per_step"] * 1e-3
         slow = max(rr["passes"], key=lambda q: q["ms"]) if rr["passes"] else None
+        es = 4
+        pass_bytes = 2 * c["M"] * int(np.prod(c["ps"], dtype=object)) * es
         tf32 = {"gflops": flops / sec / 1e9, "ms_per_step": rr["ms_per_step"], "passes": rr["passes"],
                 "hbm_frac_slowest_pass": (pass_bytes / (slow["ms"] * 1e-3) / 1e9 / peaks.get("hbm_gbs")) if slow else None,
                 "tolerance": "5e-3 of the row maximum (TF32 operands, fp32 accumulation)",
@@ -463,7 +587,7 @@ def run_single(args):
 
     cpu = None
     if not args.no_cpu:
-        cpu = cpu_sample(c, cpu_rows_for(c), reps=2)
+        cpu = cpu_whole(c, reps=2, warm=1)
         cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
 
     out = {
@@ -472,7 +596,9 @@ def run_single(args):
         "vs_baseline": None, "dtype": c["dt"], "data": "synthetic", "config": workload_desc(c, 1),
         "value_harness_count": flops_harness(c) / (r["ms_per_step"] * 1e-3) / 1e9,
         "gpu_launches": r["launches"], "passes": passes, "clocks": clocks, "roofline": roof, "e2e": e2e,
-        "cpu_baseline": cpu, "fma_peak_tflops": fma_peak, "configs": extra, "tf32_optin": tf32,
+        "cpu_baseline": cpu, "parity_rows_max_rel_err": parity,
+        "fma_peak_tflops": {"probe": fma_probe, "device_props": fma_props}, "configs": extra, "tf32_optin": tf32,
+        "gemm_timeouts": int(fk.get().fkbGemmTmaTimeouts()),
     }
     print(json.dumps(out))
 
@@ -493,8 +619,8 @@ def main():
         return run_reference(args)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1 or args.gpus > 1:
-        from fastkron_b200 import mg_bench
-        return mg_bench.run(args, CONFIGS, globals())
+        import bench_mg
+        return bench_mg.run(args, CONFIGS, globals())
     return run_single(args)
 
 

@@ -11,7 +11,7 @@ import numpy as np
 
 def _fill_block(x, c, M, K, Kl, rank):
     """Local [M, Kl] block of the seeded global X: element (m, j) is stream index m*K + rank*Kl + j."""
-    from . import synth
+    from fastkron_b200 import synth
     xv = x.view(M, Kl)
     for m in range(M):
         synth.fill_uniform_cuda(xv[m], c["seed"], offset=m * K + rank * Kl)
@@ -20,8 +20,8 @@ def _fill_block(x, c, M, K, Kl, rank):
 def run(args, CONFIGS, B):
     import torch
     import torch.distributed as dist
-    from . import mg, synth
-    from . import lib as fk
+    from fastkron_b200 import mg, synth
+    from fastkron_b200 import lib as fk
     import ctypes
 
     rank = int(os.environ.get("RANK", "0"))

@@ -318,6 +318,10 @@ class HostGeMKM:
                 out_done[b] = self.s_out.record_event()
         cur.wait_stream(self.s_out)
         cur.wait_stream(self.s_mm)
+        # z_host is host memory the caller reads with the CPU: block until the last slab landed
+        for ev in out_done:
+            if ev is not None:
+                ev.synchronize()
         return z_host
 
     def close(self):

@@ -4,6 +4,8 @@
 #include "engine.h"
 
 #include <sstream>
+#include <stdio.h>
+#include <string.h>
 
 namespace fkb {
 
@@ -80,6 +82,18 @@ static std::string planKey(const Problem& pr, const PlanOptions& o) {
      << (int)pr.opF << ':' << pr.forward << ':' << o.fusion << o.haveT2 << o.forceGeneric << ':' << o.align;
   for (uint32_t i = 0; i < pr.N; i++) os << ':' << pr.P[i] << 'x' << pr.Q[i];
   return os.str();
+}
+
+// 0 = silent, 1 = INFO, 2 = DEBUG; read once from FASTKRON_LOG.
+static int logLevel() {
+  static const int lv = [] {
+    const char* e = getenv("FASTKRON_LOG");
+    if (!e) return 0;
+    if (!strcmp(e, "INFO") || !strcmp(e, "info")) return 1;
+    if (!strcmp(e, "DEBUG") || !strcmp(e, "debug")) return 2;
+    return 0;
+  }();
+  return lv;
 }
 
 static int ptrAlign(const void* p) {
@@ -167,6 +181,9 @@ fastKronError Engine::run(Problem pr, const CallOperands& ops) {
         if (tB > 0.f && tA > 0.f && tB < tA) plan = other;
       }
     }
+    // FASTKRON_LOG=INFO (or DEBUG): one block per newly planned problem, as the reference prints
+    // its chosen kernel series (src/env/env.cpp:57-65, src/handle/handle.cpp:160-170).
+    if (logLevel() >= 1) fprintf(stderr, "[FastKron] plan %s\n%s", key.c_str(), plan.describe().c_str());
     it = planCache_.emplace(key, std::move(plan)).first;
   }
   const Plan& plan = it->second;

@@ -50,6 +50,7 @@ class Engine {
   fastKronError setStream(void* ptrToStream);
   bool cudaReady() const { return cudaReady_; }
   cudaStream_t stream() const { return stream_; }
+  int device() const { return device_; }       // device that was current at initCUDA
   // SMs a launch may plan for: the device's count scaled by the handle's share (see
   // setSmShare); persistent kernels size their grids from it.
   int smCount() const { int n = (int)(smCount_ * smShare_ + 0.5f); return n < 1 ? 1 : n; }

@@ -73,7 +73,8 @@ static fastKronError launchGemmOne(const Pass& ps, const LaunchCtx& cx, int mode
   if (a.numTiles >= (1ull << 31) / C::NCH) return fastKronKernelNotFound;   // 32-bit tile counters
 
   auto kern = gemmPassKernel<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT, UNR, MINB, PACK>;
-  static int ctasPerSm = 0;
+  static int ctasPerSmDev[kMaxDevices] = {0};
+  int& ctasPerSm = ctasPerSmDev[currentDeviceSlot()];
   if (ctasPerSm == 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
     if (e != cudaSuccess) return cudaToFk(e);

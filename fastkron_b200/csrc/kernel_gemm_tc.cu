@@ -386,7 +386,8 @@ static fastKronError launchOne(const Pass& ps, const LaunchCtx& cx) {
 
   const size_t smem = (size_t)P * P * 4 + (size_t)NS * P * kRows * 4 + 1024;
   auto kern = gemmTf32Kernel<P, XT>;
-  static bool attr = false;
+  static bool attrDev[kMaxDevices] = {false};
+  bool& attr = attrDev[currentDeviceSlot()];
   if (!attr) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { cudaGetLastError(); return fastKronKernelNotFound; }

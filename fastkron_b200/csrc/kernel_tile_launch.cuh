@@ -36,7 +36,8 @@ static fastKronError launchTileOne(const Pass& ps, const LaunchCtx& cx) {
 
   const size_t smem = (size_t)R * SUB * es + (size_t)NF * P * P * es + kTileMaxR * sizeof(unsigned long long);
   auto kern = tilePassKernel<T, P, NF, WIDE>;
-  static bool attrSet = false;
+  static bool attrSetDev[kMaxDevices] = {false};
+  bool& attrSet = attrSetDev[currentDeviceSlot()];
   if (!attrSet) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return cudaToFk(e);
@@ -84,7 +85,8 @@ static fastKronError launchTileTrOne(const Pass& ps, const LaunchCtx& cx) {
   if (a.numSuper == 0) return fastKronSuccess;
   const size_t smem = (size_t)mT * aT * G * es + (size_t)NF * P * P * es + 2 * kTileMaxR * sizeof(unsigned long long);
   auto kern = tileTransposeKernel<T, P, NF, TR>;
-  static bool attrSet = false;
+  static bool attrSetDev[kMaxDevices] = {false};
+  bool& attrSet = attrSetDev[currentDeviceSlot()];
   if (!attrSet) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
     if (e != cudaSuccess) return cudaToFk(e);

@@ -56,6 +56,16 @@ fastKronError launchGemmTf32(const Pass& ps, const LaunchCtx& cx);   // only rea
 bool tileSupported(DType dt, uint32_t P, int nf, int tileB);
 bool gemmSupported(DType dt, uint32_t P, uint32_t Q, uint64_t B);
 
+// Function attributes (the opt-in to more than 48 KB of dynamic shared memory) and occupancy
+// answers belong to one device: a launcher that caches them keeps one slot per device ordinal,
+// indexed by the device that is current at the launch.
+constexpr int kMaxDevices = 64;
+inline int currentDeviceSlot() {
+  int d = 0;
+  if (cudaGetDevice(&d) != cudaSuccess) { cudaGetLastError(); return 0; }
+  return (d >= 0 && d < kMaxDevices) ? d : 0;
+}
+
 inline fastKronError cudaToFk(cudaError_t e) {
   if (e == cudaSuccess) return fastKronSuccess;
   if (e == cudaErrorIllegalAddress) return fastKronInvalidMemoryAccess;

@@ -36,7 +36,6 @@ constexpr size_t kMaxTmp = FASTKRON_NOALLOC_MAX_TEMP_ELEMS;
 // temp1 = first half, temp2 = second half
 static __device__ __align__(256) float gNoAllocScratch[2 * kMaxTmp];
 
-constexpr int kMaxDevices = 64;
 // Device address of gNoAllocScratch per device ordinal.  The symbol's name is only a
 // host-side handle: kernels must be given the address cudaGetSymbolAddress returns for
 // the device that is current.
@@ -70,6 +69,12 @@ extern "C" fastKronError sgemkmNoAlloc(fastKronHandle handle, uint32_t M, uint32
 
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return fastKronOtherError;
+  // The handle's stream belongs to the device that was current at fastKronInitCUDA; the scratch
+  // address is per device, so the two must agree.
+  if (dev != e->device()) {
+    fprintf(stderr, "sgemkmNoAlloc: current device %d is not the handle's device %d\n", dev, e->device());
+    return fastKronInvalidArgument;
+  }
   if (gScratchAddr[dev] == nullptr) {
     // once per device, with that device current
     float* p = nullptr;

@@ -35,6 +35,29 @@ int fkbFillUniformF64(double* dst, uint64_t n, uint64_t seed, uint64_t offset, v
 }
 }
 
+// The same streams on the host (multi-threaded), for operands that start in host memory.
+extern "C" {
+void fkbFillUniformHostF32(float* dst, uint64_t n, uint64_t seed, uint64_t offset) {
+#pragma omp parallel for schedule(static)
+  for (long long i = 0; i < (long long)n; i++) dst[i] = (float)fkbUniformPm1(seed, offset + (uint64_t)i);
+}
+void fkbFillUniformHostF64(double* dst, uint64_t n, uint64_t seed, uint64_t offset) {
+#pragma omp parallel for schedule(static)
+  for (long long i = 0; i < (long long)n; i++) dst[i] = fkbUniformPm1(seed, offset + (uint64_t)i);
+}
+// FP32 / FP64 FMA peak of a device from its properties, in TFLOP/s:
+// SMs x lanes x 2 x maximum SM clock, with 128 FP32 and 64 FP64 lanes per SM on compute
+// capability 10.x.  Returns 0 when the device cannot be queried.
+double fkbSimtPeakFromProps(int device, int isDouble) {
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { cudaGetLastError(); return 0.0; }
+  int khz = 0;
+  if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device) != cudaSuccess) { cudaGetLastError(); return 0.0; }
+  const double lanes = isDouble ? 64.0 : 128.0;
+  return (double)prop.multiProcessorCount * lanes * 2.0 * (double)khz * 1e3 / 1e12;
+}
+}
+
 // ---- arithmetic peak probes (used by bench.py for the FP32 / FP64 rooflines) --------
 // Each thread runs 16 independent FMA chains; the result is stored so the work is kept.
 template <typename T>

@@ -14,6 +14,10 @@ import os
 
 import numpy as np
 
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SYNTH_PATH = os.path.join(_HERE, "libfkb_synth.so")
+_slib = None
+
 _C = np.uint64(0xD1342543DE82EF95)
 _G = np.uint64(0x9E3779B97F4A7C15)
 _M1 = np.uint64(0xBF58476D1CE4E5B9)
@@ -36,9 +40,24 @@ def _unit(seed, n, offset):
     return (h >> np.uint64(11)).astype(np.float64) * (1.0 / 9007199254740992.0)
 
 
-def uniform(seed, n, dtype=np.float32, offset=0, chunk=1 << 24):
-    """n values uniform in [-1, 1) as a 1-D numpy array."""
+def _helper():
+    """The helper library (csrc/synth.cu), or None when it has not been built."""
+    global _slib
+    if _slib is None and os.path.exists(_SYNTH_PATH):
+        _slib = ctypes.CDLL(_SYNTH_PATH)
+    return _slib
+
+
+def uniform(seed, n, dtype=np.float32, offset=0, chunk=1 << 24, force_numpy=False):
+    """n values uniform in [-1, 1) as a 1-D numpy array.  Large requests go through the
+    multi-threaded C generator of the helper library when it is there (same bits)."""
     out = np.empty(n, dtype=dtype)
+    lib = None if (force_numpy or n < (1 << 20)) else _helper()
+    if lib is not None and hasattr(lib, "fkbFillUniformHostF32") and np.dtype(dtype) in (np.float32, np.float64):
+        fn = lib.fkbFillUniformHostF32 if np.dtype(dtype) == np.float32 else lib.fkbFillUniformHostF64
+        fn.restype = None
+        fn(ctypes.c_void_p(out.ctypes.data), ctypes.c_uint64(n), ctypes.c_uint64(seed), ctypes.c_uint64(offset))
+        return out
     for s in range(0, n, chunk):
         m = min(chunk, n - s)
         out[s:s + m] = (_unit(seed, m, offset + s) * 2.0 - 1.0).astype(dtype)
@@ -56,20 +75,13 @@ def normal(seed, n, dtype=np.float32, offset=0, chunk=1 << 23):
     return out
 
 
-_HERE = os.path.dirname(os.path.abspath(__file__))
-_SYNTH_PATH = os.path.join(_HERE, "libfkb_synth.so")
-_slib = None
-
 
 def fill_uniform_cuda(t, seed, offset=0):
     """Fill the contiguous CUDA tensor t (float32/float64) with uniform(seed) values,
     element i of the flattened tensor getting stream index offset+i."""
     import torch
-    global _slib
-    if _slib is None:
-        if not os.path.exists(_SYNTH_PATH):
-            raise ImportError("%s is missing -- run `make -C fastkron_b200/csrc`" % _SYNTH_PATH)
-        _slib = ctypes.CDLL(_SYNTH_PATH)
+    if _helper() is None:
+        raise ImportError("%s is missing -- run `make -C fastkron_b200/csrc`" % _SYNTH_PATH)
     assert t.is_cuda and t.is_contiguous()
     fn = _slib.fkbFillUniformF32 if t.dtype == torch.float32 else _slib.fkbFillUniformF64
     rc = fn(ctypes.c_void_p(t.data_ptr()), ctypes.c_uint64(t.numel()), ctypes.c_uint64(seed),

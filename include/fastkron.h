@@ -124,7 +124,10 @@ fastKronError gekmmSizes(fastKronHandle handle, uint32_t M, uint32_t N,
 
 /* GeMKM arguments (reference: include/fastkron.h:284-296): M rows, N factors of shape
  * Ps[i] x Qs[i]; temp1 must not be NULL; temp2 may be NULL unless Z aliases Y or Z is
- * smaller than a temporary -- with temp2 NULL the library uses Z as its second scratch. */
+ * smaller than a temporary -- with temp2 NULL the library uses Z as its second scratch, so Z
+ * must then hold the tmpElems that gekmmSizes reports, which exceeds M*L whenever an
+ * intermediate is wider than the result (shrinking factors, P > Q).  The library cannot see
+ * the size of Z and does not check this. */
 #define FASTKRON_GEMKM_ARGS(T)                                                    \
   fastKronHandle handle, fastKronBackend backend,                                 \
   uint32_t M, uint32_t N, uint32_t Ps[], uint32_t Qs[],                           \

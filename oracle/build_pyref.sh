@@ -8,11 +8,12 @@
 #
 # Test infrastructure only; everything lands in oracle/_ref/ (git-ignored build output).
 #
-# usage: oracle/build_pyref.sh [reference_dir]
+# usage: oracle/build_pyref.sh <reference_dir>   (or FASTKRON_REFERENCE_DIR)
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 REPO="$(dirname "$HERE")"
-REF="${1:-/root/reference}"
+REF="${1:-${FASTKRON_REFERENCE_DIR:-}}"
+[ -n "$REF" ] || { echo "usage: $0 <reference_dir> (or set FASTKRON_REFERENCE_DIR)" >&2; exit 2; }
 OUT="$HERE/_ref"
 [ -f "$REF/pyfastkron/pywrapper.cpp" ] || { echo "reference tree not found at $REF" >&2; exit 2; }
 [ -f "$OUT/libFastKron.so" ] || { echo "run oracle/build_ref.sh first" >&2; exit 2; }
@@ -35,4 +36,7 @@ g++ -O2 -shared -fPIC -std=c++17 $INC -DENABLE_CUDA "$REF/pyfastkron/pywrapper.c
 ln -sf libFastKron.so "$OUT/libFastKronRefX86.so"
 g++ -O2 -shared -fPIC -std=c++17 $INC -DENABLE_X86 "$REF/pyfastkron/pywrapper.cpp" \
     -I"$REF/include" -L"$OUT" -lFastKronRefX86 -Wl,-rpath,'$ORIGIN/..' -o "$PKG/FastKronX86$SUF"
+# the reference's own torch test, byte for byte, for tests/test_pyfastkron_rebind_gpu.py
+mkdir -p "$OUT/pytests"
+cp "$REF/tests/python/test_torch.py" "$OUT/pytests/test_torch.py"
 echo "built $PKG"

@@ -12,10 +12,11 @@
 # baseline -march=x86-64-v2: every kernel TU raises its own ISA level with a
 # "#pragma GCC target", src/config.h:25-31).
 #
-# usage: oracle/build_ref.sh [reference_dir] [jobs]
+# usage: oracle/build_ref.sh <reference_dir> [jobs]   (or FASTKRON_REFERENCE_DIR)
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-REF="${1:-/root/reference}"
+REF="${1:-${FASTKRON_REFERENCE_DIR:-}}"
+[ -n "$REF" ] || { echo "usage: $0 <reference_dir> (or set FASTKRON_REFERENCE_DIR)" >&2; exit 2; }
 JOBS="${2:-$(nproc)}"
 OUT="$HERE/_ref"
 WORK="${FASTKRON_REF_BUILD_DIR:-${TMPDIR:-/tmp}/fastkron_ref_build}"

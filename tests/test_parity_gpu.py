@@ -305,6 +305,9 @@ FULL = [
     ("C2", cases.case("mkm", "f64", 16, [8] * 8, [8] * 8, seed=1)),
     ("C3", cases.case("kmm", "f32", 1024, [32] * 3, [32] * 3, "T", "N", 2.0, 1.0, seed=2, dist="normal")),
     ("C4", cases.case("mkm", "f32", 2048, [128, 128, 16], [128, 128, 16], seed=4)),
+    # the one configuration whose element offsets reach 2^32 (M*K = 2^32): X, Z and both
+    # temporaries are 17 GB each
+    ("C5", cases.case("mkm", "f32", 256, [64] * 4, [64] * 4, seed=5)),
 ]
 
 
@@ -351,14 +354,23 @@ def test_full_size_rows_and_checksum(h, name, c):
     want = oracle.port_gekmm("mkm", xr, fs, ps, qs, len(rows), "N", opf_mkm, c["alpha"], c["beta"], yr)
     got = Zv[rows].cpu().numpy()
     assert cases.row_rel_err(got, want, "mkm") <= cases.TOL[c["dt"]]
-    # checksum over all rows, accumulated in float64 on the device
+    # checksum over all rows, accumulated in float64 on the device, a slab of rows at a time so
+    # that the float64 copies stay below 2 GB whatever the configuration
+    del t1, t2
+    torch.cuda.empty_cache()
     w = torch.from_numpy(_rowsum_weights(fs, ps, qs, mm, c["opf"], c["dt"])).cuda()
-    lhs = Zv.double().sum(dim=1)
-    rhs = c["alpha"] * (Xv.double() @ w)
-    if Yv is not None:
-        rhs = rhs + c["beta"] * Yv.double().sum(dim=1)
-    scale = Zv.double().abs().sum(dim=1)
-    rel = ((lhs - rhs).abs() / scale).max().item()
+    slab = max(1, min(M, (1 << 28) // max(K, Lc)))
+    rel = 0.0
+    for r0 in range(0, M, slab):
+        r1 = min(M, r0 + slab)
+        zs = Zv[r0:r1].double()
+        lhs = zs.sum(dim=1)
+        rhs = c["alpha"] * (Xv[r0:r1].double() @ w)
+        if Yv is not None:
+            rhs = rhs + c["beta"] * Yv[r0:r1].double().sum(dim=1)
+        scale = zs.abs().sum(dim=1)
+        rel = max(rel, ((lhs - rhs).abs() / scale).max().item())
+        del zs, lhs, rhs, scale
     assert rel <= cases.TOL[c["dt"]], rel
 
 
