@@ -7,6 +7,7 @@ same plan, so the results are compared exactly as well as against the usual tole
 on two calls in a row -- the second call finds the static scratch dirty from the first.
 """
 import ctypes
+import gc
 import os
 import sys
 
@@ -50,10 +51,17 @@ def test_no_alloc_matches_sgemkm_twice():
             ye, te = h.sizes(c["M"], c["ps"], c["qs"])
             assert te <= fk.NOALLOC_MAX_TEMP_ELEMS
             z = torch.full((ye,), float("nan"), dtype=torch.float32, device="cuda")
+            # nothing may be allocated by the call: neither through torch's allocator nor behind its
+            # back (cudaMemGetInfo sees every allocation on the device).  Collect garbage first so
+            # that tensors of earlier tests are not released in the middle of the measurement.
+            gc.collect()
+            torch.cuda.synchronize()
             before = torch.cuda.memory_allocated()
+            free_before = torch.cuda.mem_get_info()[0]
             assert _call_noalloc(h, c, xd, fd, z, yd) == fk.SUCCESS
             torch.cuda.synchronize()
             assert torch.cuda.memory_allocated() == before
+            assert torch.cuda.mem_get_info()[0] >= free_before
             got = z.cpu().numpy().reshape(want.shape)
             assert cases.row_rel_err(got, want, "mkm") <= cases.TOL["f32"]
             assert np.array_equal(got, want)
