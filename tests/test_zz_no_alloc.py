@@ -41,6 +41,7 @@ def test_no_alloc_matches_sgemkm_twice():
     # two different problems back to back; both fit the static scratch
     problems = [cases.case("mkm", "f32", 16, [16] * 4, [16] * 4, "N", "N", 2.0, 1.0, seed=51),
                 cases.case("mkm", "f32", 7, [8, 4, 32, 3], [8, 4, 32, 5], "N", "T", 1.0, 0.0, seed=52)]
+    first = True
     for rep in range(2):
         for c in problems:
             x, fs, y = cases.operands(c)
@@ -61,7 +62,11 @@ def test_no_alloc_matches_sgemkm_twice():
             assert _call_noalloc(h, c, xd, fd, z, yd) == fk.SUCCESS
             torch.cuda.synchronize()
             assert torch.cuda.memory_allocated() == before
-            assert torch.cuda.mem_get_info()[0] >= free_before
+            # (the very first call on a device may make the driver load the module that holds the
+            # static scratch -- CUDA loads modules lazily -- which is when those 16 MiB are mapped)
+            if not first:
+                assert torch.cuda.mem_get_info()[0] >= free_before
+            first = False
             got = z.cpu().numpy().reshape(want.shape)
             assert cases.row_rel_err(got, want, "mkm") <= cases.TOL["f32"]
             assert np.array_equal(got, want)
