@@ -1,10 +1,14 @@
 """bench.py's N > 1 leg: the column-sharded GeMKM with one process per GPU (torchrun).
 
-Strong scaling: the same problem as at N = 1, X's columns split over the ranks.  Timing is
-on the device (CUDA events on the compute stream), bracketed by a barrier and a device
-synchronisation on both sides, maximum over ranks; rank 0 prints the JSON line."""
+Strong scaling: the same problem as at N = 1, X's columns split over the ranks.  A step is one
+complete product: every rank's result block is complete (in device order) before the next
+step's first exchange touches a buffer.  Timing is on the device (CUDA events on the compute
+stream), bracketed by a barrier and a device synchronisation on both sides, maximum over
+ranks; rank 0 prints the JSON line."""
+import ctypes
 import json
 import os
+import time
 
 import numpy as np
 
@@ -17,12 +21,62 @@ def _fill_block(x, c, M, K, Kl, rank):
         synth.fill_uniform_cuda(xv[m], c["seed"], offset=m * K + rank * Kl)
 
 
+def _c_api_blocking_ms(c, world, fs_host, reps=3):
+    """Rank 0 alone: the reference's own entry point fastKronMgSGEMM (one process driving all
+    GPUs, blocking) on the same problem; wall-clock milliseconds per call."""
+    import torch
+    from fastkron_b200 import lib as fk
+    L = fk.get()
+    M, ps, qs = c["M"], c["ps"], c["qs"]
+    n = len(ps)
+    K = int(np.prod(ps, dtype=object))
+    Lc = int(np.prod(qs, dtype=object))
+    Kl = K // world
+    h = ctypes.c_void_p()
+    fk.check(L.fastKronInit(ctypes.byref(h), ctypes.c_uint32(fk.BACKEND_CUDA)))
+    streams, xs, res, t1, t2, fd = [], [], [], [], [], []
+    try:
+        for d in range(world):
+            with torch.cuda.device(d):
+                streams.append(torch.cuda.Stream())
+        sarr = (ctypes.c_void_p * world)(*[s.cuda_stream for s in streams])
+        fk.check(L.fastKronMgInitCUDA(h, sarr, world, 1, world, 1))
+        ye, te = ctypes.c_size_t(), ctypes.c_size_t()
+        fk.check(L.gekmmSizes(h, ctypes.c_uint32(M), ctypes.c_uint32(n), fk.u32arr(ps), fk.u32arr(qs),
+                              ctypes.byref(ye), ctypes.byref(te)))
+        for d in range(world):
+            with torch.cuda.device(d):
+                x = torch.empty(M * Kl, dtype=torch.float32, device="cuda")
+                _fill_block(x, c, M, K, Kl, d)
+                xs.append(x)
+                res.append(torch.empty(ye.value, dtype=torch.float32, device="cuda"))
+                t1.append(torch.empty(te.value, dtype=torch.float32, device="cuda"))
+                t2.append(torch.empty(te.value, dtype=torch.float32, device="cuda"))
+                fd.append([torch.from_numpy(f).cuda() for f in fs_host])
+                torch.cuda.synchronize()
+        P = lambda ts: (ctypes.c_void_p * world)(*[t.data_ptr() for t in ts])
+        kron = (ctypes.c_void_p * (world * n))(*[fd[d][i].data_ptr() for d in range(world) for i in range(n)])
+        times = []
+        for it in range(1 + reps):
+            t0 = time.perf_counter()
+            fk.check(L.fastKronMgSGEMM(h, ctypes.c_uint32(n), P(xs), kron, P(res), ctypes.c_uint32(M),
+                                       ctypes.c_uint32(Lc), ctypes.c_uint32(K), fk.u32arr(qs), fk.u32arr(ps),
+                                       P(t1), P(t2), sarr))
+            if it > 0:
+                times.append((time.perf_counter() - t0) * 1e3)
+        row0 = torch.cat([r.view(M, Lc // world)[0].to("cuda:0") for r in res]).cpu().numpy()
+        return float(np.mean(times)), float(min(times)), row0
+    finally:
+        L.fastKronDestroy(h)
+        del xs, res, t1, t2, fd
+        torch.cuda.set_device(0)
+
+
 def run(args, CONFIGS, B):
     import torch
     import torch.distributed as dist
     from fastkron_b200 import mg, synth
     from fastkron_b200 import lib as fk
-    import ctypes
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -33,6 +87,7 @@ def run(args, CONFIGS, B):
     torch.cuda.set_device(local)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    host_group = dist.new_group(backend="gloo")          # host-side barriers that keep the GPUs idle
     c = dict(CONFIGS[args.config], name=args.config)
     if c["mm"] != "mkm" or c["dt"] != "f32" or c["beta"] != 0:
         raise SystemExit("the multi-GPU path is fp32 GeMKM without epilogue (as in the reference)")
@@ -41,139 +96,150 @@ def run(args, CONFIGS, B):
     Lc = int(np.prod(qs, dtype=object))
     Kl, Ll = K // world, Lc // world
 
-    # Transport chosen from measurements on this pool (8 B200 on NVSwitch): at 4 and 8 ranks the
-    # copy-engine exchange with two staggered row slices wins (8 ranks: 7.2 ms against 9.5 ms per
-    # step); at 2 ranks half of every block stays local and storing straight from the kernels wins.
-    mode = os.environ.get("FASTKRON_MG_MODE", "staged" if world >= 4 else "fused")
-    parts = int(os.environ.get("FASTKRON_MG_PARTS", "2" if mode == "staged" else "1"))
-    eng = mg.PipelinedRankGeMKM(M, ps, qs, parts=parts, mode=mode)
-    x = torch.empty(M * Kl, dtype=torch.float32, device="cuda")
-    _fill_block(x, c, M, K, Kl, rank)
-    fs = [torch.from_numpy(synth.uniform(c["seed"] + 2000 + i, p * q, np.float32)).cuda()
-          for i, (p, q) in enumerate(zip(ps, qs))]
-    L = fk.get()
-    L.fkbLaunchCount.restype = ctypes.c_ulonglong
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        eng = mg.PipelinedRankGeMKM(M, ps, qs, parts=0, mode="auto")
+        x = torch.empty(M * Kl, dtype=torch.float32, device="cuda")
+        _fill_block(x, c, M, K, Kl, rank)
+        fs_host = [synth.uniform(c["seed"] + 2000 + i, p * q, np.float32) for i, (p, q) in enumerate(zip(ps, qs))]
+        fs = [torch.from_numpy(f).cuda() for f in fs_host]
+        L = fk.get()
+        L.fkbLaunchCount.restype = ctypes.c_ulonglong
 
-    for _ in range(args.warmup):
-        eng.run(x, fs)
-    torch.cuda.synchronize()
-    dist.barrier()
-    sampler = B["ClockSampler"](local) if rank == 0 else None
-    if sampler:
-        sampler.start()
-    n0 = L.fkbLaunchCount()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    dist.barrier()
-    e0.record()
-    for st in range(args.steps):
-        eng.run(x, fs, join=(st == 0))       # slices stay staggered from one step to the next
-    eng.join()
-    e1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    launches = int(L.fkbLaunchCount() - n0)
-    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    clocks = sampler.stop() if sampler else None
-    ms_step = float(ms.item()) / args.steps
-    flops = B["flops_library"](c)
-    value = flops / (ms_step * 1e-3) / 1e9
-
-    # ---- end to end: host block -> device, product, device -> host, every step ---------
-    # Rows are independent, so the rank's block is cut into row chunks and pipelined on three
-    # streams: chunk i+1 travels host->device while chunk i is multiplied (a collective step of
-    # all ranks on that chunk) and chunk i-1 travels device->host.
-    hx = torch.empty(M * Kl, dtype=torch.float32, pin_memory=True)
-    hz = torch.empty(M * Ll, dtype=torch.float32, pin_memory=True)
-    hx.copy_(x)
-    torch.cuda.synchronize()
-    nc = int(os.environ.get("FASTKRON_E2E_CHUNKS", "16"))
-    while nc > 1 and M % nc != 0:
-        nc //= 2
-    Mc = M // nc
-    # the chunk engine stores straight into the peers from its kernels (the transfers of a chunk
-    # are small next to its PCIe copies, so the copy-engine transport of the timed loop above
-    # has nothing to add here)
-    eng_e = mg.PipelinedRankGeMKM(Mc, ps, qs, parts=1, mode="fused") if nc > 1 else eng
-    xd = [torch.empty(Mc * Kl, dtype=torch.float32, device="cuda") for _ in range(2)]
-    zd = [torch.empty(Mc * Ll, dtype=torch.float32, device="cuda") for _ in range(2)]
-    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    hxv, hzv = hx.view(M, Kl), hz.view(M, Ll)
-
-    def e2e_step():
-        cur = torch.cuda.current_stream()
-        s_in.wait_stream(cur)
-        s_out.wait_stream(cur)
-        ev_mm, ev_out = [None, None], [None, None]
-        for ci in range(nc):
-            b = ci & 1
-            with torch.cuda.stream(s_in):
-                if ev_mm[b] is not None:
-                    s_in.wait_event(ev_mm[b])                  # xd[b] has been consumed
-                xd[b].view(Mc, Kl).copy_(hxv[ci * Mc:(ci + 1) * Mc], non_blocking=True)
-                ev_in = s_in.record_event()
-            cur.wait_event(ev_in)
-            if ev_out[b] is not None:
-                cur.wait_event(ev_out[b])                      # zd[b] has been copied out
-            off = 0
-            for zp in eng_e.run(xd[b], fs):
-                zd[b][off:off + zp.numel()].copy_(zp.reshape(-1))
-                off += zp.numel()
-            ev_mm[b] = cur.record_event()
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_mm[b])
-                hzv[ci * Mc:(ci + 1) * Mc].copy_(zd[b].view(Mc, Ll), non_blocking=True)
-                ev_out[b] = s_out.record_event()
-        cur.wait_stream(s_out)
-
-    e2e_steps = max(1, min(args.steps, 3))
-    tt = []
-    for it in range(1 + e2e_steps):
-        dist.barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        e2e_step()
-        b.record()
+        for _ in range(args.warmup):
+            eng.run(x, fs)
         torch.cuda.synchronize()
-        t = torch.tensor([a.elapsed_time(b)], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        if it > 0:
-            tt.append(float(t.item()))
-    e2e_ms = float(np.mean(tt))
-    if eng_e is not eng:
-        eng_e.close()
-    del xd, zd
+        dist.barrier()
+        sampler = B["ClockSampler"](local) if rank == 0 else None
+        if sampler:
+            sampler.start()
+        n0 = L.fkbLaunchCount()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for st in range(args.steps):
+            eng.run(x, fs)
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        launches = int(L.fkbLaunchCount() - n0)
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        clocks = sampler.stop() if sampler else None
+        ms_step = float(ms.item()) / args.steps
+        flops = B["flops_library"](c)
+        value = flops / (ms_step * 1e-3) / 1e9
 
-    # ---- parity spot check outside the timed region: two full rows against the oracle ----
-    z = torch.cat(eng.run(x, fs), dim=0)
+        # ---- one call at a time, host-synchronised on both sides (what a blocking caller sees) ----
+        tt = []
+        for it in range(1 + 5):
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            eng.run(x, fs)
+            b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b)], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if it > 0:
+                tt.append(float(t.item()))
+        single_ms = float(np.mean(tt))
+
+        # ---- end to end: host block -> device, product, device -> host, every step ---------
+        hx = torch.empty(M * Kl, dtype=torch.float32, pin_memory=True)
+        hz = torch.empty(M * Ll, dtype=torch.float32, pin_memory=True)
+        hx.copy_(x)
+        torch.cuda.synchronize()
+        e2e_steps = max(1, min(args.steps, 3))
+        tt, copy_tt = [], []
+        for it in range(1 + e2e_steps):
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            eng.run_host(hx, fs, hz)
+            b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b)], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if it > 0:
+                tt.append(float(t.item()))
+        e2e_ms = float(np.mean(tt))
+        # the copies alone, all ranks at once (what the host's memory system and the PCIe links give)
+        xd2 = torch.empty_like(x)
+        for it in range(3):
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            xd2.copy_(hx, non_blocking=True)
+            b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b)], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if it > 0:
+                copy_tt.append(float(t.item()))
+        h2d_alone_ms = float(np.mean(copy_tt))
+        del xd2
+
+        # ---- parity spot check outside the timed region: two full rows against the oracle ----
+        z = eng.run(x, fs).clone()
+        torch.cuda.synchronize()
+        e2e_same = bool(torch.equal(hz.view(M, Ll)[M - 1].cuda(), z.view(M, Ll)[M - 1]) and
+                        torch.equal(hz.view(M, Ll)[0].cuda(), z.view(M, Ll)[0]))
+        check = None
+        rows = [0, M - 1]
+        xr = [torch.empty(len(rows) * Kl, dtype=torch.float32, device="cuda") for _ in range(world)]
+        zr = [torch.empty(len(rows) * Ll, dtype=torch.float32, device="cuda") for _ in range(world)]
+        dist.all_gather(xr, x.view(M, Kl)[rows].contiguous().view(-1))
+        dist.all_gather(zr, z.view(M, Ll)[rows].contiguous().view(-1))
+        zfull = None
+        if rank == 0 and not args.no_cpu:
+            import oracle
+            xfull = np.concatenate([t.cpu().numpy().reshape(len(rows), Kl) for t in xr], axis=1)
+            zfull = np.concatenate([t.cpu().numpy().reshape(len(rows), Ll) for t in zr], axis=1)
+            want = oracle.port_gekmm("mkm", xfull, fs_host, ps, qs, len(rows))
+            den = np.abs(want).max(axis=1, keepdims=True)
+            check = float((np.abs(zfull.astype(np.float64) - want) / den).max())
+        parts, mode = eng.parts, eng.mode
+        eng.close()
+        del x, z, xr, zr
+        torch.cuda.empty_cache()
+
+    # ---- the reference's own entry point, one process driving all GPUs (rank 0, others idle) ----
     torch.cuda.synchronize()
-    # the pipelined host path must have produced the same rows
-    e2e_same = bool(torch.equal(hz.view(M, Ll)[M - 1].cuda(), z.view(M, Ll)[M - 1]))
-    check = None
-    rows = [0, M - 1]
-    xr = [torch.empty(len(rows) * Kl, dtype=torch.float32, device="cuda") for _ in range(world)]
-    zr = [torch.empty(len(rows) * Ll, dtype=torch.float32, device="cuda") for _ in range(world)]
-    dist.all_gather(xr, x.view(M, Kl)[rows].contiguous().view(-1))
-    dist.all_gather(zr, z[rows].contiguous().view(-1))
-    if rank == 0 and not args.no_cpu:
-        import oracle
-        xfull = np.concatenate([t.cpu().numpy().reshape(len(rows), Kl) for t in xr], axis=1)
-        zfull = np.concatenate([t.cpu().numpy().reshape(len(rows), Ll) for t in zr], axis=1)
-        want = oracle.port_gekmm("mkm", xfull, [f.cpu().numpy() for f in fs], ps, qs, len(rows))
-        den = np.abs(want).max(axis=1, keepdims=True)
-        check = float((np.abs(zfull.astype(np.float64) - want) / den).max())
+    dist.barrier(group=host_group)
+    c_api = None
+    if rank == 0:
+        try:
+            mean_ms, min_ms, row0 = _c_api_blocking_ms(c, world, fs_host)
+            c_api = {"ms_per_call": mean_ms, "ms_min": min_ms, "gflops": flops / (mean_ms * 1e-3) / 1e9,
+                     "how": "fastKronMgSGEMM (blocking, one process, %d devices), wall clock around the call, mean of 3 after 1 warm-up" % world,
+                     "row0_equals_per_rank_result": bool(zfull is not None and np.array_equal(row0, zfull[0])) if zfull is not None else None}
+        except Exception as ex:          # report, do not lose the line
+            c_api = {"error": str(ex)[:300]}
+    dist.barrier(group=host_group)
 
     if rank == 0:
         peaks, peak_src = B["read_measured_peaks"]()
-        fma_peak = B["measure_fma_peak"]("f32")
+        fma_probe = B["measure_fma_peak"]("f32")
+        fma_props = B["simt_peak_from_props"]("f32")
+        fp_peak = max(fma_probe, fma_props)
         per_gpu_tflops = value / world / 1e3
-        roof = {"bound": "fp32_simt", "achieved": per_gpu_tflops, "peak": fma_peak, "unit": "TFLOP/s",
-                "frac": per_gpu_tflops / fma_peak if fma_peak else None, "traffic": None,
-                "peak_source": "FMA-chain probe in this run", "kernel": "gemm",
-                "note": "whole-step rate per GPU (4 passes + 2 in-kernel exchanges + 2 barriers)",
-                "nvlink": {"bytes_per_gpu_per_step": 2 * (world - 1) * M * Kl * 4 // world,
-                           "gbs_per_direction": 2 * (world - 1) * M * Kl * 4 / world / (ms_step * 1e-3) / 1e9,
+        nv_bytes = 2 * (world - 1) * M * Kl * 4 // world
+        roof = {"bound": "fp32_simt", "achieved": per_gpu_tflops, "peak": fp_peak, "unit": "TFLOP/s",
+                "frac": per_gpu_tflops / fp_peak if fp_peak else None, "traffic": None,
+                "peak_source": "larger of the FMA-chain probe of this run (%.1f) and SMs x lanes x 2 x max SM clock (%.1f)" % (fma_probe, fma_props),
+                "kernel": "gemm",
+                "note": "whole-step rate per GPU (4 passes + 2 exchanges)",
+                "nvlink": {"bytes_per_gpu_per_step": nv_bytes,
+                           "gbs_per_direction": nv_bytes / (ms_step * 1e-3) / 1e9,
                            "measured_peer_copy_gbs": 770.0}}
         out = {
             "metric": "GeMKM/GeKMM GFLOP/s", "value": value, "unit": "GFLOP/s", "n_gpus": world,
@@ -182,17 +248,21 @@ def run(args, CONFIGS, B):
             "config": B["workload_desc"](c, world),
             "value_harness_count": B["flops_harness"](c) / (ms_step * 1e-3) / 1e9,
             "gpu_launches": launches * world, "clocks": clocks, "roofline": roof,
+            "single_call_ms": single_ms,
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
                     "h2d_bytes_per_step": M * Kl * 4 * world, "d2h_bytes_per_step": M * Ll * 4 * world,
-                    "ms_per_step": e2e_ms, "steps": e2e_steps, "row_chunks": nc,
-                    "how": "row chunks pipelined: copy-in, collective product and copy-out overlap",
+                    "ms_per_step": e2e_ms, "steps": e2e_steps, "row_slices": parts,
+                    "how": "each rank's pinned block: a row slice is copied in ahead of its passes and copied out when complete",
+                    "h2d_alone_ms_all_ranks": h2d_alone_ms,
+                    "h2d_alone_gbs_aggregate": M * Kl * 4 * world / (h2d_alone_ms * 1e-3) / 1e9,
                     "matches_device_result": e2e_same},
             "cpu_baseline": None, "parity_rows_max_rel_err": check,
-            "row_slices": eng.parts, "exchange_mode": eng.mode,
-            "exchange": ("2 all-to-alls per step; staged: kernels fill local per-destination blocks, copy engines "
-                         "ship them over NVLink; fused: the producing kernels store into the peers; barriers = "
-                         "1-element NCCL all-reduce, stream-ordered"),
+            "row_slices": parts, "exchange_mode": mode, "c_api_single_process": c_api,
+            "exchange": ("2 all-to-alls per step; staged: kernels fill local per-destination blocks, copy engines ship "
+                         "them over NVLink; fused: the producing kernels store into the peers; ranks are ordered by "
+                         "32-bit sequence flags in device memory (stream memory operations), no collective library "
+                         "in the timed region"),
         }
         print(json.dumps(out), flush=True)
-    eng.close()
+    dist.barrier(group=host_group)
     dist.destroy_process_group()

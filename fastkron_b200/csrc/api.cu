@@ -269,23 +269,6 @@ int fkbGetPassTimes(fastKronHandle handle, float* ms, int* kinds, int maxN) {
   return E(handle)->passTimes(ms, kinds, maxN);
 }
 
-// Share of the GPU (0 < share <= 1) that launches of this handle size their grids for.
-// Two handles on two streams with share 0.5 each run side by side, which lets a pass that
-// is bound by NVLink stores overlap with a pass that is bound by arithmetic.
-int fkbSetSmShare(fastKronHandle handle, float share) {
-  if (!handle) return (int)fastKronInvalidArgument;
-  E(handle)->setSmShare(share);
-  return 0;
-}
-
-// Upper bound on the tiles one CTA of the large-factor kernel processes (0 = persistent
-// CTAs).  A bound makes CTAs retire often, which lets small kernels of other streams in.
-int fkbSetTilesPerCta(fastKronHandle handle, int n) {
-  if (!handle) return (int)fastKronInvalidArgument;
-  E(handle)->setTilesPerCta(n);
-  return 0;
-}
-
 // ---- introspection used by the host-side tests (not part of the reference ABI) --
 // Writes the textual plan of a problem into buf; returns the number of passes
 // or a negative fastKronError.

@@ -51,15 +51,8 @@ class Engine {
   bool cudaReady() const { return cudaReady_; }
   cudaStream_t stream() const { return stream_; }
   int device() const { return device_; }       // device that was current at initCUDA
-  // SMs a launch may plan for: the device's count scaled by the handle's share (see
-  // setSmShare); persistent kernels size their grids from it.
-  int smCount() const { int n = (int)(smCount_ * smShare_ + 0.5f); return n < 1 ? 1 : n; }
-  // Let two handles that work concurrently on different streams each take a part of the
-  // GPU: share in (0, 1].
-  void setSmShare(float s) { smShare_ = (s > 0.f && s <= 1.f) ? s : 1.f; }
-  // See LaunchCtx::tilesPerCta.
-  void setTilesPerCta(int n) { tilesPerCta_ = n > 0 ? n : 0; }
-  int tilesPerCta() const { return tilesPerCta_; }
+  // SMs of the handle's device; persistent kernels size their grids from it.
+  int smCount() const { return smCount_; }
   // fastKronOptionsTF32 on the handle, or FASTKRON_TF32=1 in the environment (read once).
   bool tf32Enabled() const {
     static const bool env = [] { const char* e = getenv("FASTKRON_TF32"); return e && e[0] == '1'; }();
@@ -101,8 +94,6 @@ class Engine {
   cudaStream_t stream_ = nullptr;
   int device_ = 0;
   int smCount_ = 148;
-  float smShare_ = 1.f;
-  int tilesPerCta_ = 0;
   std::map<std::string, Plan> planCache_;
 };
 

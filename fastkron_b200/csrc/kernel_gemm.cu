@@ -90,10 +90,6 @@ static fastKronError launchGemmOne(const Pass& ps, const LaunchCtx& cx, int mode
       encodeInputMap<T>(&tmap, a.X, a.numChunks, P, a.B, TJ, PC))
     a.useTma = 1;
   unsigned long long grid = (unsigned long long)cx.smCount * ctasPerSm;
-  if (cx.tilesPerCta > 0) {
-    const unsigned long long want = (a.numTiles + cx.tilesPerCta - 1) / cx.tilesPerCta;
-    if (want > grid) grid = want;
-  }
   if (grid > a.numTiles) grid = a.numTiles;
   kern<<<(unsigned)grid, C::THREADS, C::SMEM, cx.stream>>>(a, tmap);
   return cudaToFk(cudaGetLastError());

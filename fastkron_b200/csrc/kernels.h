@@ -35,10 +35,6 @@ struct LaunchCtx {
   // Gemm launcher only: input rows split as [outer][chunk][pSplit][B] (see GemmArgs)
   unsigned pSplit = 0;
   unsigned long long pOuter = 0, nStride = 0;
-  // Gemm launcher: 0 = persistent CTAs (one per slot, looping over all tiles); n > 0 = at most
-  // n tiles per CTA, so that CTAs retire every few tens of microseconds and a small kernel
-  // from another stream (a collective used as a barrier) can get onto the GPU in between.
-  int tilesPerCta = 0;
   // Gemm launcher: opt-in TF32 tensor-core kernel for fp32 passes (fastKronOptionsTF32)
   bool tf32 = false;
 };

@@ -1,5 +1,5 @@
-// Multi-GPU GeMKM: the entry points of include/fastkronMg.h plus a per-rank form of the
-// same two phases for one-process-per-GPU hosts.
+// Multi-GPU GeMKM: the entry points of include/fastkronMg.h and, for hosts that run one
+// process per GPU, the same schedule per rank (fkbMgPipe*).
 //
 // Distribution (same as the reference, src/handle/distrib_handle.cu:52-414 and
 // src/handle/handle.cpp:411-416): GPU (r, c) of a gpusInM x gpusInK grid owns rows
@@ -8,22 +8,33 @@
 // column block is a range of the leading index p1.
 //
 //   phase 1  every GPU contracts modes N..2 of its block [M][P1/GK][P2..PN] locally.  The
-//            pass that applies factor 2 does not write locally: output row (m, p1, q2)
-//            goes to GPU q2 / (Q2/GK), which thereby receives [M][P1][Q2/GK][Q3..QN] --
-//            all of p1, a slice of q2.  This is the all-to-all of the reference
-//            (ncclSend/ncclRecv + pack/unpack kernels, distrib_handle.cu:276-347, or its
-//            P2P store variant, src/kernels/cuda/global-store.cuh:1-25) fused into the
-//            producing kernel as plain 128-bit peer stores over NVLink.
-//   barrier  all GPUs of the row group finished phase 1.
-//   phase 2  every GPU contracts mode 1 of what it received; output row (m, q1) goes to
-//            GPU q1 / (Q1/GK) at its canonical place [M][Q1/GK][Q2][Q3..QN], again by peer
-//            stores from the producing kernel.
-//   barrier  the result blocks are complete.
+//            pass that applies factor 2 hands its output over: row (m, p1, q2) belongs to
+//            GPU q2 / (Q2/GK), which thereby receives [M][P1][Q2/GK][Q3..QN] -- all of p1,
+//            a slice of q2.  (The all-to-all of the reference: ncclSend/ncclRecv plus pack and
+//            unpack kernels, distrib_handle.cu:276-347, or its P2P store variant,
+//            src/kernels/cuda/global-store.cuh:1-25.)
+//   phase 2  every GPU contracts mode 1 of what it received; row (m, q1) belongs to GPU
+//            q1 / (Q1/GK) at its canonical place [M][Q1/GK][Q2][Q3..QN].
 //
-// Two exchanges are the minimum for a column-sharded input and output.  Nothing here waits
-// inside a kernel: ordering is by stream events (one process) or by a collective the host
-// enqueues between the phases (one process per GPU), so the code is safe to emulate with
-// several logical GPUs on one device.  No TMA multicast, no device-side flags.
+// Two exchanges are the minimum for a column-sharded input and output.  Two transports:
+//   fused   the producing kernel stores every output row straight into the owner's buffer
+//           (128-bit peer stores).  Any factor shape.
+//   staged  the producing kernel fills per-destination blocks in local memory and the copy
+//           engines ship them (cudaMemcpyAsync / cudaMemcpy2DAsync on side streams), so the
+//           NVLink traffic needs no SM.  Needs the large-factor kernel for phase 2.
+// The rows are cut into `parts` independent slices that run out of phase: while one slice's
+// blocks travel, another slice computes (rows never communicate, so a slice is a complete
+// small problem).  Enqueue order on the one compute stream of a GPU:
+//   P1(0), P1(1), P2(0), P1(2), P2(1), ..., P2(parts-1).
+//
+// Ordering between GPUs never happens inside a kernel.  One process driving all GPUs
+// (fastKronMgSGEMM) uses CUDA events across devices.  One process per GPU cannot (an event
+// wait captures whatever record the waiting process has seen, and processes do not see each
+// other's calls), so there every rank owns a small array of 32-bit sequence flags in device
+// memory that its peers map through CUDA IPC: a sender's stream writes the call's sequence
+// number into the receiver's flag after its copies (cuStreamWriteValue32), the receiver's
+// stream waits for it (cuStreamWaitValue32) -- stream-ordered memory operations executed by
+// the GPU's front end, no SM, no kernel, no collective library.  No TMA multicast anywhere.
 //
 // Requirements: N >= 2 when GK > 1, and GK divides P1, Q1 and Q2 (the reference has the
 // analogous divisibility rules, src/kmm/kmmalgo.cpp:51-70).  fp32, row-major, opX = opF = N
@@ -33,37 +44,17 @@
 #include "gemm_table.h"
 #include "fastkronMg.h"
 
+#include <cuda.h>
+
+#include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
+#include <memory>
 #include <vector>
 
 namespace fkb {
 
-struct MgState {
-  int gpus = 1, gm = 1, gk = 1;
-  bool oneDevice = false;                 // all logical GPUs live on the current device (emulation)
-  std::vector<int> device;                // physical device of logical GPU g
-  std::vector<cudaStream_t> stream;
-  std::vector<int> smCount;
-  std::vector<cudaEvent_t> ev1, ev2;
-};
-
-void mgAdjustSizes(const MgState* mg, const Problem& pr, size_t* yElems, size_t* tmpElems) {
-  // per-device counts; the temporary is doubled: its second half is the receive area of the
-  // first exchange (the reference doubles it for its NCCL staging, src/handle/handle.cpp:327-338)
-  const uint64_t rows = pr.M / mg->gm;
-  const uint64_t cols = (pr.N == 1) ? (pr.K() > pr.L() ? pr.K() : pr.L()) : pr.maxIntermediateCols();
-  *yElems = (size_t)(rows * (pr.L() / mg->gk));
-  *tmpElems = (size_t)(rows * (cols / mg->gk)) * (mg->gk > 1 ? 2 : 1);
-}
-
-void mgDestroy(MgState* mg) {
-  if (!mg) return;
-  for (cudaEvent_t e : mg->ev1) cudaEventDestroy(e);
-  for (cudaEvent_t e : mg->ev2) cudaEventDestroy(e);
-  delete mg;
-}
-
-// ---- the two phases for one rank --------------------------------------------------------
+// ---- one rank's view of the problem -------------------------------------------------------
 
 struct MgRank {
   int g = 0, gk = 1;                      // column rank, column-group size
@@ -104,11 +95,12 @@ static void mgScatter2(const MgRank& r, Scatter* sc) {
   sc->zOff = (long long)(r.g * q2loc * B);
 }
 
-// Phase 1: modes N..2 of the local block; the last pass redistributes into recvPeers[d].
-// stage: 0 = all passes, 1 = only the local passes, 2 = only the redistributing pass.
-// packed: destination blocks hold only this rank's rows, [M][P1/G][Q2/G][B] (staged form).
+// Phase 1: modes N..2 of the local block; the last pass hands its rows to bases[d].
+// packed == false: bases[d] is rank d's receive area laid out [M][P1][Q2/G][B] (fused
+// transport).  packed == true: bases[d] is a block that holds only this rank's rows,
+// [M][P1/G][Q2/G][B] (staged transport).
 static fastKronError mgPhase1(Engine* e, const MgRank& r, const float* x, const float* const* Fs, float* t1,
-                              float* t2, void* const recvPeers[], int stage = 0, bool packed = false) {
+                              float* t2, void* const bases[], bool packed) {
   fastKronError err = mgCheck(r);
   if (err != fastKronSuccess) return err;
   const uint32_t p1loc = r.Ps[0] / r.gk;
@@ -126,12 +118,11 @@ static fastKronError mgPhase1(Engine* e, const MgRank& r, const float* x, const 
   for (size_t k = 0; k < plan.passes.size(); k++) {
     Pass ps = plan.passes[k];
     const bool last = (k + 1 == plan.passes.size());
-    if ((stage == 1 && last) || (stage == 2 && !last)) continue;
     LaunchCtx cx;
-    cx.stream = r.stream; cx.dt = DType::F32; cx.smCount = r.smCount; cx.tilesPerCta = e->tilesPerCta();
+    cx.stream = r.stream; cx.dt = DType::F32; cx.smCount = r.smCount;
     auto buf = [&](Buf b) -> void* {
       switch (b) { case Buf::X: return const_cast<float*>(x); case Buf::T1: return t1; case Buf::T2: return t2;
-                   default: return recvPeers[r.g]; }
+                   default: return bases[r.g]; }
     };
     cx.src = buf(ps.src);
     cx.dst = buf(ps.dst);
@@ -146,7 +137,7 @@ static fastKronError mgPhase1(Engine* e, const MgRank& r, const float* x, const 
         cx.scatter.sM = (long long)(cx.scatter.aLoc * cx.scatter.qPer) * cx.scatter.sQ;   // P1/G rows per m
         cx.scatter.zOff = 0;
       }
-      for (int d = 0; d < r.gk; d++) cx.scatter.base[d] = recvPeers[d];
+      for (int d = 0; d < r.gk; d++) cx.scatter.base[d] = bases[d];
     }
     err = e->launchPass(ps, cx);
     if (err != fastKronSuccess) return err;
@@ -154,7 +145,8 @@ static fastKronError mgPhase1(Engine* e, const MgRank& r, const float* x, const 
   return fastKronSuccess;
 }
 
-// Phase 2: mode 1 of the received tensor [M][P1][Q2/GK * Q3..QN]; rows go to resultPeers[d].
+// Phase 2, fused transport: mode 1 of the received tensor [M][P1][Q2/GK * Q3..QN]; rows go
+// to resultPeers[d].
 static fastKronError mgPhase2(Engine* e, const MgRank& r, const float* recv, const float* F0,
                               void* const resultPeers[]) {
   fastKronError err = mgCheck(r);
@@ -167,13 +159,349 @@ static fastKronError mgPhase2(Engine* e, const MgRank& r, const float* recv, con
   ps.zsM = (int64_t)(r.Qs[0] * B2); ps.zsA = ps.zsM; ps.zsG = (int64_t)B2; ps.zsB = 1;
   ps.kind = gemmEligible(DType::F32, r.Ps[0], r.Qs[0], B2) ? KernelKind::Gemm : KernelKind::Generic;
   LaunchCtx cx;
-  cx.stream = r.stream; cx.dt = DType::F32; cx.smCount = r.smCount; cx.tilesPerCta = e->tilesPerCta();
+  cx.stream = r.stream; cx.dt = DType::F32; cx.smCount = r.smCount;
   cx.src = recv; cx.dst = resultPeers[r.g];
   cx.F[0] = F0;
   factorStrides(MMType::MKM, fastKronOp_N, ps.P[0], ps.Q[0], &cx.fsP, &cx.fsQ);
   mgScatter2(r, &cx.scatter);
   for (int d = 0; d < r.gk; d++) cx.scatter.base[d] = resultPeers[d];
   return e->launchPass(ps, cx);
+}
+
+// True when the staged transport can run the problem: phase 2 reads its input as received,
+// [sender][M][P1/G][B2], which only the large-factor kernel's split-input mode does.
+static bool mgStagedEligible(const MgRank& r) {
+  if (r.gk < 2 || r.N < 2) return false;
+  const uint64_t B2 = (r.Qs[1] / r.gk) * prodQ(r, 2);
+  return gemmEligible(DType::F32, r.Ps[0], r.Qs[0], B2) && B2 % (uint64_t)gemmTileJ(DType::F32) == 0;
+}
+
+// Phase 2, staged transport: output block d = [M][Q1/G][B2] for rank d at stage2 + d*blk2.
+static fastKronError mgPhase2Staged(Engine* e, const MgRank& r, const float* recv, const float* F0, float* stage2) {
+  if (!mgStagedEligible(r)) return fastKronKernelNotFound;
+  const uint64_t p1loc = r.Ps[0] / r.gk, q1loc = r.Qs[0] / r.gk;
+  const uint64_t B2 = (r.Qs[1] / r.gk) * prodQ(r, 2);
+  Pass ps;
+  ps.f0 = 0; ps.nf = 1; ps.M = r.M; ps.A = 1; ps.B = B2;
+  ps.P[0] = r.Ps[0]; ps.Q[0] = r.Qs[0];
+  ps.xsM = (int64_t)(r.Ps[0] * B2); ps.xsA = ps.xsM; ps.xsG = (int64_t)B2; ps.xsB = 1;
+  ps.zsM = (int64_t)(r.Qs[0] * B2); ps.zsA = ps.zsM; ps.zsG = (int64_t)B2; ps.zsB = 1;
+  ps.kind = KernelKind::Gemm;
+  LaunchCtx cx;
+  cx.stream = r.stream; cx.dt = DType::F32; cx.smCount = r.smCount;
+  cx.src = recv; cx.dst = stage2;
+  cx.F[0] = F0;
+  factorStrides(MMType::MKM, fastKronOp_N, ps.P[0], ps.Q[0], &cx.fsP, &cx.fsQ);
+  cx.pSplit = (unsigned)p1loc; cx.pOuter = (unsigned long long)r.M * p1loc * B2; cx.nStride = p1loc * B2;
+  cx.scatter.parts = r.gk; cx.scatter.qPer = q1loc; cx.scatter.aLoc = 1;
+  cx.scatter.sM = (long long)(q1loc * B2); cx.scatter.sA = 0; cx.scatter.sQ = (long long)B2; cx.scatter.zOff = 0;
+  const uint64_t blk = (uint64_t)r.M * q1loc * B2;
+  for (int d = 0; d < r.gk; d++) cx.scatter.base[d] = stage2 + (size_t)d * blk;
+  return e->launchPass(ps, cx);
+}
+
+// ---- stream memory operations (driver API, fetched at run time) ---------------------------
+
+typedef CUresult (*StreamValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+struct StreamMemOps {
+  StreamValue32Fn write = nullptr, wait = nullptr;
+  bool ok() const { return write && wait; }
+};
+static const StreamMemOps& streamMemOps() {
+  static StreamMemOps ops = [] {
+    StreamMemOps o;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      o.write = reinterpret_cast<StreamValue32Fn>(p);
+    else
+      cudaGetLastError();
+    p = nullptr;
+    if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      o.wait = reinterpret_cast<StreamValue32Fn>(p);
+    else
+      cudaGetLastError();
+    return o;
+  }();
+  return ops;
+}
+
+// ---- the pipelined schedule of one rank ---------------------------------------------------
+
+// Number of row slices: FASTKRON_MG_PARTS when set (a supported knob), else by the size of the
+// rank's block -- slices below a few tens of MB only add launches and copies.
+static int mgDefaultParts(uint64_t rows, uint64_t blockElems) {
+  int want;
+  if (const char* e = getenv("FASTKRON_MG_PARTS")) want = atoi(e);
+  else want = blockElems >= (1ull << 27) ? 4 : (blockElems >= (1ull << 24) ? 2 : 1);
+  if (want < 1) want = 1;
+  if (want > 16) want = 16;
+  while (want > 1 && rows % (uint64_t)want != 0) want--;
+  return want;
+}
+
+struct MgPipe {
+  Engine* eng = nullptr;
+  int device = 0;
+  MgRank rank;                            // rank.M = rows of ONE slice
+  std::vector<uint32_t> Ps, Qs;
+  int parts = 1;
+  bool staged = false;
+  bool useFlags = false;                  // one process per GPU: order by sequence flags
+  uint64_t Kloc = 0, Lloc = 0, blk1 = 0, blk2 = 0, B2 = 0;
+  uint64_t tmpSlice = 0, recvSlice = 0;   // elements per slice
+  // local buffers (owned when `owned`, else the caller's)
+  bool owned = false;
+  float *t1 = nullptr, *t2 = nullptr, *stage1 = nullptr, *recv = nullptr, *result = nullptr, *xdev = nullptr;
+  uint32_t* flags = nullptr;              // [2][parts][gk], only with useFlags
+  // peers' buffers as this process can address them (index = column rank)
+  void* recvPeer[kMaxParts] = {nullptr};
+  void* resultPeer[kMaxParts] = {nullptr};
+  uint32_t* flagPeer[kMaxParts] = {nullptr};
+  bool peersSet = false;
+  cudaStream_t compute = nullptr;
+  cudaStream_t copy[2] = {nullptr, nullptr};
+  cudaStream_t h2d = nullptr, d2h = nullptr;
+  std::vector<cudaEvent_t> evC2, evC3, evX1, evX2, evIn;
+  uint32_t seq = 0;
+  MgPipe* const* group = nullptr;         // one process: the pipes of this row group, by column rank
+
+  size_t flagIndex(int phase, int slice, int src) const { return ((size_t)phase * parts + slice) * rank.gk + src; }
+};
+
+static void mgPipeDestroy(MgPipe* p) {
+  if (!p) return;
+  int cur = 0;
+  cudaGetDevice(&cur);
+  cudaSetDevice(p->device);
+  for (auto* v : {&p->evC2, &p->evC3, &p->evX1, &p->evX2, &p->evIn})
+    for (cudaEvent_t e : *v) cudaEventDestroy(e);
+  for (cudaStream_t s : {p->copy[0], p->copy[1], p->h2d, p->d2h})
+    if (s) cudaStreamDestroy(s);
+  if (p->owned) {
+    for (float* b : {p->t1, p->t2, p->stage1, p->recv, p->result, p->xdev})
+      if (b) cudaFree(b);
+  }
+  if (p->flags) cudaFree(p->flags);
+  cudaSetDevice(cur);
+  delete p;
+}
+
+// Streams and events of a pipe; the device must be current.
+static fastKronError mgPipeInitStreams(MgPipe* p) {
+  int lo = 0, hi = 0;
+  cudaDeviceGetStreamPriorityRange(&lo, &hi);
+  for (int i = 0; i < 2; i++)
+    if (cudaStreamCreateWithPriority(&p->copy[i], cudaStreamNonBlocking, hi) != cudaSuccess) return fastKronOtherError;
+  if (cudaStreamCreateWithPriority(&p->h2d, cudaStreamNonBlocking, hi) != cudaSuccess) return fastKronOtherError;
+  if (cudaStreamCreateWithPriority(&p->d2h, cudaStreamNonBlocking, hi) != cudaSuccess) return fastKronOtherError;
+  for (auto* v : {&p->evC2, &p->evC3, &p->evX1, &p->evX2, &p->evIn}) {
+    for (int s = 0; s < p->parts; s++) {
+      cudaEvent_t ev;
+      if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return fastKronOtherError;
+      v->push_back(ev);
+    }
+  }
+  return fastKronSuccess;
+}
+
+// Geometry of a pipe from (rows per rank, factor shapes, group size, slices).
+static fastKronError mgPipeGeometry(MgPipe* p, int g, int gk, uint32_t rows, uint32_t N, const uint32_t* Ps,
+                                    const uint32_t* Qs, int parts, int wantStaged) {
+  p->Ps.assign(Ps, Ps + N);
+  p->Qs.assign(Qs, Qs + N);
+  p->rank.g = g; p->rank.gk = gk; p->rank.N = N; p->rank.Ps = p->Ps.data(); p->rank.Qs = p->Qs.data();
+  p->rank.M = rows;
+  fastKronError err = mgCheck(p->rank);
+  if (err != fastKronSuccess) return err;
+  if (gk < 2) return fastKronInvalidArgument;
+  uint64_t K = 1, L = 1;
+  for (uint32_t i = 0; i < N; i++) { K *= Ps[i]; L *= Qs[i]; }
+  p->Kloc = K / gk; p->Lloc = L / gk;
+  if (parts < 1 || rows % (uint32_t)parts != 0) return fastKronInvalidArgument;
+  p->parts = parts;
+  p->rank.M = rows / parts;
+  const bool can = mgStagedEligible(p->rank);
+  if (wantStaged == 1 && !can) return fastKronKernelNotFound;
+  p->staged = wantStaged == 0 ? false : can;
+  const uint64_t B = prodQ(p->rank, 2);
+  const uint64_t p1loc = Ps[0] / gk, q1loc = Qs[0] / gk, q2loc = Qs[1] / gk;
+  p->B2 = q2loc * B;
+  p->blk1 = (uint64_t)p->rank.M * p1loc * q2loc * B;
+  p->blk2 = (uint64_t)p->rank.M * q1loc * p->B2;
+  // widest local intermediate per slice = the global one divided by the group size
+  Problem full;
+  full.N = N;
+  for (uint32_t i = 0; i < N; i++) { full.P[i] = Ps[i]; full.Q[i] = Qs[i]; }
+  const uint64_t cols = N == 1 ? (K > L ? K : L) : full.maxIntermediateCols();
+  p->tmpSlice = (uint64_t)p->rank.M * (cols / gk);
+  p->recvSlice = (uint64_t)p->rank.M * Ps[0] * p->B2;
+  return fastKronSuccess;
+}
+
+// ---- ordering primitives --------------------------------------------------------------------
+// signal(phase, slice) on `s`: this rank's outgoing blocks of that slice and phase have landed.
+// With flags, the signal towards rank d is written right after the copy to d (see the copies).
+static fastKronError mgSignalAll(MgPipe* p, int phase, int slice, cudaStream_t s) {
+  std::vector<cudaEvent_t>& ev = phase == 0 ? p->evX1 : p->evX2;
+  if (cudaEventRecord(ev[slice], s) != cudaSuccess) return fastKronOtherError;
+  return fastKronSuccess;
+}
+static fastKronError mgFlagTo(MgPipe* p, int phase, int slice, int d, cudaStream_t s) {
+  if (!p->useFlags) return fastKronSuccess;
+  const StreamMemOps& ops = streamMemOps();
+  uint32_t* addr = p->flagPeer[d] + p->flagIndex(phase, slice, p->rank.g);
+  if (ops.write((CUstream)s, (CUdeviceptr)(uintptr_t)addr, p->seq, 0) != CUDA_SUCCESS) return fastKronOtherError;
+  return fastKronSuccess;
+}
+// `s` waits until every OTHER rank's blocks of (phase, slice) have landed here.
+static fastKronError mgWaitAll(MgPipe* p, int phase, int slice, cudaStream_t s) {
+  const int G = p->rank.gk, g = p->rank.g;
+  if (p->useFlags) {
+    const StreamMemOps& ops = streamMemOps();
+    for (int d = 0; d < G; d++) {
+      if (d == g) continue;
+      uint32_t* addr = p->flags + p->flagIndex(phase, slice, d);
+      if (ops.wait((CUstream)s, (CUdeviceptr)(uintptr_t)addr, p->seq, 0 /* >= */) != CUDA_SUCCESS) return fastKronOtherError;
+    }
+    return fastKronSuccess;
+  }
+  for (int d = 0; d < G; d++) {
+    if (d == g) continue;
+    MgPipe* q = p->group[d];
+    cudaEvent_t ev = phase == 0 ? q->evX1[slice] : q->evX2[slice];
+    if (cudaStreamWaitEvent(s, ev, 0) != cudaSuccess) return fastKronOtherError;
+  }
+  return fastKronSuccess;
+}
+
+// ---- the two halves of a slice --------------------------------------------------------------
+
+static fastKronError mgEnqueueP1(MgPipe* p, int s, const float* x, const float* const* Fs) {
+  const int G = p->rank.gk, g = p->rank.g;
+  MgRank r = p->rank;
+  r.stream = p->compute;
+  float* t1 = p->t1 + (size_t)s * p->tmpSlice;
+  float* t2 = p->t2 + (size_t)s * p->tmpSlice;
+  float* recvS = (float*)p->recvPeer[g] + (size_t)s * p->recvSlice;
+  const float* xs = x + (size_t)s * r.M * p->Kloc;
+  void* bases[kMaxParts];
+  if (p->staged) {
+    float* st = p->stage1 + (size_t)s * p->tmpSlice;
+    for (int d = 0; d < G; d++) bases[d] = st + (size_t)d * p->blk1;
+    bases[g] = recvS + (size_t)g * p->blk1;          // this rank's own block needs no transport
+  } else {
+    for (int d = 0; d < G; d++) bases[d] = (float*)p->recvPeer[d] + (size_t)s * p->recvSlice;
+  }
+  fastKronError err = mgPhase1(p->eng, r, xs, Fs, t1, t2, bases, p->staged);
+  if (err != fastKronSuccess) return err;
+  if (cudaEventRecord(p->evC2[s], p->compute) != cudaSuccess) return fastKronOtherError;
+  cudaStream_t cs = p->staged ? p->copy[s & 1] : p->compute;
+  if (p->staged) {
+    if (cudaStreamWaitEvent(cs, p->evC2[s], 0) != cudaSuccess) return fastKronOtherError;
+    for (int k = 1; k < G; k++) {
+      const int d = (g + k) % G;
+      float* dst = (float*)p->recvPeer[d] + (size_t)s * p->recvSlice + (size_t)g * p->blk1;
+      if (cudaMemcpyAsync(dst, bases[d], p->blk1 * sizeof(float), cudaMemcpyDeviceToDevice, cs) != cudaSuccess)
+        return fastKronOtherError;
+      if ((err = mgFlagTo(p, 0, s, d, cs)) != fastKronSuccess) return err;
+    }
+  } else {
+    for (int k = 1; k < G; k++)
+      if ((err = mgFlagTo(p, 0, s, (g + k) % G, cs)) != fastKronSuccess) return err;
+  }
+  return mgSignalAll(p, 0, s, cs);
+}
+
+static fastKronError mgEnqueueP2(MgPipe* p, int s, const float* F0) {
+  const int G = p->rank.gk, g = p->rank.g;
+  MgRank r = p->rank;
+  r.stream = p->compute;
+  fastKronError err = mgWaitAll(p, 0, s, p->compute);
+  if (err != fastKronSuccess) return err;
+  const float* recvS = (const float*)p->recvPeer[g] + (size_t)s * p->recvSlice;
+  const uint64_t q1loc = p->Qs[0] / G;
+  const size_t resSlice = (size_t)s * r.M * p->Lloc;            // rows of this slice in a result block
+  cudaStream_t cs = p->staged ? p->copy[s & 1] : p->compute;
+  if (p->staged) {
+    float* st2 = p->t1 + (size_t)s * p->tmpSlice;               // free again: every local pass of the slice is done
+    err = mgPhase2Staged(p->eng, r, recvS, F0, st2);
+    if (err != fastKronSuccess) return err;
+    if (cudaEventRecord(p->evC3[s], p->compute) != cudaSuccess) return fastKronOtherError;
+    if (cudaStreamWaitEvent(cs, p->evC3[s], 0) != cudaSuccess) return fastKronOtherError;
+    const size_t rows = (size_t)r.M * q1loc, width = p->B2 * sizeof(float), dpitch = (size_t)G * width;
+    for (int k = 0; k < G; k++) {
+      const int d = (g + k) % G;
+      float* dst = (float*)p->resultPeer[d] + resSlice + (size_t)g * p->B2;
+      if (cudaMemcpy2DAsync(dst, dpitch, st2 + (size_t)d * p->blk2, width, width, rows, cudaMemcpyDeviceToDevice,
+                            cs) != cudaSuccess)
+        return fastKronOtherError;
+      if (d != g && (err = mgFlagTo(p, 1, s, d, cs)) != fastKronSuccess) return err;
+    }
+  } else {
+    void* res[kMaxParts];
+    for (int d = 0; d < G; d++) res[d] = (float*)p->resultPeer[d] + resSlice;
+    err = mgPhase2(p->eng, r, recvS, F0, res);
+    if (err != fastKronSuccess) return err;
+    for (int k = 1; k < G; k++)
+      if ((err = mgFlagTo(p, 1, s, (g + k) % G, cs)) != fastKronSuccess) return err;
+  }
+  return mgSignalAll(p, 1, s, cs);
+}
+
+// `stream` waits until slice s of this rank's result block is complete: its own outgoing
+// copies are done and every peer's rows have arrived.
+static fastKronError mgWaitResult(MgPipe* p, int s, cudaStream_t stream) {
+  if (cudaStreamWaitEvent(stream, p->evX2[s], 0) != cudaSuccess) return fastKronOtherError;
+  return mgWaitAll(p, 1, s, stream);
+}
+
+// The enqueue order of a call as (half, slice) pairs: P1(0), then P1(i), P2(i-1), ..., P2(last).
+static void mgOrder(int parts, std::vector<std::pair<int, int>>* order) {
+  order->clear();
+  order->push_back({1, 0});
+  for (int i = 1; i < parts; i++) { order->push_back({1, i}); order->push_back({2, i - 1}); }
+  order->push_back({2, parts - 1});
+}
+
+// ---- multi-GPU state of a handle (one process driving all GPUs) ----------------------------
+
+struct MgState {
+  int gpus = 1, gm = 1, gk = 1;
+  bool oneDevice = false;                 // all logical GPUs live on the current device (emulation)
+  std::vector<int> device;                // physical device of logical GPU g
+  std::vector<cudaStream_t> stream;
+  std::vector<int> smCount;
+  std::vector<cudaEvent_t> ev1, ev2;
+  // pipes of the last problem (index = logical GPU), rebuilt when the problem changes
+  std::vector<MgPipe*> pipes;
+  std::string pipeKey;
+};
+
+void mgAdjustSizes(const MgState* mg, const Problem& pr, size_t* yElems, size_t* tmpElems) {
+  // per-device counts; the temporary is doubled: the second halves are the receive area of the
+  // first exchange and the staging area of the transport (the reference doubles it for its
+  // NCCL staging, src/handle/handle.cpp:327-338)
+  const uint64_t rows = pr.M / mg->gm;
+  const uint64_t cols = (pr.N == 1) ? (pr.K() > pr.L() ? pr.K() : pr.L()) : pr.maxIntermediateCols();
+  *yElems = (size_t)(rows * (pr.L() / mg->gk));
+  *tmpElems = (size_t)(rows * (cols / mg->gk)) * (mg->gk > 1 ? 2 : 1);
+}
+
+static void mgDropPipes(MgState* mg) {
+  for (MgPipe* p : mg->pipes) mgPipeDestroy(p);
+  mg->pipes.clear();
+  mg->pipeKey.clear();
+}
+
+void mgDestroy(MgState* mg) {
+  if (!mg) return;
+  mgDropPipes(mg);
+  for (cudaEvent_t e : mg->ev1) cudaEventDestroy(e);
+  for (cudaEvent_t e : mg->ev2) cudaEventDestroy(e);
+  delete mg;
 }
 
 }  // namespace fkb
@@ -220,7 +548,7 @@ fastKronError fastKronMgInitCUDA(fastKronHandle handle, void* streams, int gpus,
     }
     mg->smCount.push_back(prop.multiProcessorCount);
   }
-  // peer access for the direct stores (reference: cuda_kernel_db.cu:83-93)
+  // peer access for the direct stores and copies (reference: cuda_kernel_db.cu:83-93)
   if (!oneDevice) {
     for (int a = 0; a < gpus; a++) {
       cudaSetDevice(a);
@@ -278,6 +606,7 @@ fastKronError fastKronMgSGEMM(fastKronHandle handle, const uint32_t NumKronMats,
   e->sizes(full, &yElems, &tmpElems);
   mgAdjustSizes(mg, full, &yElems, &tmpElems);
   const size_t half = tmpElems / 2;
+  const uint32_t rows = M / mg->gm;
 
   fastKronError err = fastKronSuccess;
   auto streamOf = [&](int g) { return st ? st[g] : mg->stream[g]; };
@@ -286,7 +615,7 @@ fastKronError fastKronMgSGEMM(fastKronHandle handle, const uint32_t NumKronMats,
     // rows only: every GPU runs the ordinary single-device plan on its rows
     for (int g = 0; g < mg->gpus && err == fastKronSuccess; g++) {
       cudaSetDevice(mg->device[g]);
-      Problem lp = full; lp.M = M / mg->gm;
+      Problem lp = full; lp.M = rows;
       PlanOptions po; po.haveT2 = true;
       Plan plan;
       err = makePlan(lp, po, &plan);
@@ -297,37 +626,67 @@ fastKronError fastKronMgSGEMM(fastKronHandle handle, const uint32_t NumKronMats,
       err = e->execute(lp, plan, ops, streamOf(g), mg->smCount[g]);
     }
   } else {
-    // phase 1 on every GPU
-    for (int g = 0; g < mg->gpus && err == fastKronSuccess; g++) {
-      cudaSetDevice(mg->device[g]);
-      const int row = g / mg->gk, col = g % mg->gk;
-      MgRank r;
-      r.g = col; r.gk = mg->gk; r.M = M / mg->gm; r.N = n; r.Ps = KronMatRows; r.Qs = KronMatCols;
-      r.stream = streamOf(g); r.smCount = mg->smCount[g];
-      void* recv[kMaxParts];
-      for (int d = 0; d < mg->gk; d++) recv[d] = (float*)temp1[row * mg->gk + d] + half;
-      err = mgPhase1(e, r, (const float*)x[g], reinterpret_cast<const float* const*>(&kronMats[(size_t)g * n]),
-                     (float*)temp1[g], (float*)temp2[g], recv);
-      if (err == fastKronSuccess && cudaEventRecord(mg->ev1[g], streamOf(g)) != cudaSuccess) err = fastKronOtherError;
+    // One pipe per GPU, kept while the problem stays the same.  Buffers are the caller's:
+    //   temp1[g] = [ t1 | receive area ],  temp2[g] = [ t2 | staging area of exchange 1 ]
+    std::string key = std::to_string(M) + ":" + std::to_string(n);
+    for (uint32_t i = 0; i < n; i++) key += ":" + std::to_string(KronMatRows[i]) + "x" + std::to_string(KronMatCols[i]);
+    if (mg->pipeKey != key) {
+      mgDropPipes(mg);
+      MgRank probe;
+      probe.g = 0; probe.gk = mg->gk; probe.M = rows; probe.N = n; probe.Ps = KronMatRows; probe.Qs = KronMatCols;
+      err = mgCheck(probe);
+      const int parts = err == fastKronSuccess ? mgDefaultParts(rows, (uint64_t)rows * (K / mg->gk)) : 1;
+      for (int g = 0; g < mg->gpus && err == fastKronSuccess; g++) {
+        cudaSetDevice(mg->device[g]);
+        MgPipe* p = new MgPipe;
+        mg->pipes.push_back(p);
+        p->eng = e; p->device = mg->device[g];
+        err = mgPipeGeometry(p, g % mg->gk, mg->gk, rows, n, KronMatRows, KronMatCols, parts, -1);
+        if (err == fastKronSuccess) err = mgPipeInitStreams(p);
+        p->rank.smCount = mg->smCount[g];
+      }
+      if (err == fastKronSuccess) mg->pipeKey = key; else mgDropPipes(mg);
     }
-    // phase 2 once the whole row group delivered
-    for (int g = 0; g < mg->gpus && err == fastKronSuccess; g++) {
-      cudaSetDevice(mg->device[g]);
-      const int row = g / mg->gk, col = g % mg->gk;
-      for (int d = 0; d < mg->gk; d++) cudaStreamWaitEvent(streamOf(g), mg->ev1[row * mg->gk + d], 0);
-      MgRank r;
-      r.g = col; r.gk = mg->gk; r.M = M / mg->gm; r.N = n; r.Ps = KronMatRows; r.Qs = KronMatCols;
-      r.stream = streamOf(g); r.smCount = mg->smCount[g];
-      void* res[kMaxParts];
-      for (int d = 0; d < mg->gk; d++) res[d] = result[row * mg->gk + d];
-      err = mgPhase2(e, r, (const float*)temp1[g] + half, (const float*)kronMats[(size_t)g * n], res);
-      if (err == fastKronSuccess && cudaEventRecord(mg->ev2[g], streamOf(g)) != cudaSuccess) err = fastKronOtherError;
+    if (err == fastKronSuccess) {
+      for (int g = 0; g < mg->gpus; g++) {
+        MgPipe* p = mg->pipes[g];
+        const int row = g / mg->gk;
+        p->compute = streamOf(g);
+        p->t1 = (float*)temp1[g]; p->t2 = (float*)temp2[g];
+        p->stage1 = (float*)temp2[g] + half;
+        p->group = &mg->pipes[(size_t)row * mg->gk];
+        for (int d = 0; d < mg->gk; d++) {
+          p->recvPeer[d] = (float*)temp1[row * mg->gk + d] + half;
+          p->resultPeer[d] = result[row * mg->gk + d];
+        }
+      }
+      std::vector<std::pair<int, int>> order;
+      mgOrder(mg->pipes[0]->parts, &order);
+      // stage-major, GPU-minor: every GPU's signal of a (phase, slice) is enqueued before any
+      // GPU's wait for it
+      for (size_t o = 0; o < order.size() && err == fastKronSuccess; o++) {
+        for (int g = 0; g < mg->gpus && err == fastKronSuccess; g++) {
+          cudaSetDevice(mg->device[g]);
+          MgPipe* p = mg->pipes[g];
+          const float* const* Fs = reinterpret_cast<const float* const*>(&kronMats[(size_t)g * n]);
+          err = order[o].first == 1 ? mgEnqueueP1(p, order[o].second, (const float*)x[g], Fs)
+                                    : mgEnqueueP2(p, order[o].second, Fs[0]);
+        }
+      }
+      for (int g = 0; g < mg->gpus && err == fastKronSuccess; g++) {
+        cudaSetDevice(mg->device[g]);
+        MgPipe* p = mg->pipes[g];
+        for (int s = 0; s < p->parts && err == fastKronSuccess; s++) err = mgWaitResult(p, s, p->compute);
+      }
     }
   }
   // the call is blocking, like the reference's (it joins its per-GPU threads)
   for (int g = 0; g < mg->gpus; g++) {
     cudaSetDevice(mg->device[g]);
     if (cudaStreamSynchronize(streamOf(g)) != cudaSuccess && err == fastKronSuccess) err = cudaToFk(cudaGetLastError());
+    if (g < (int)mg->pipes.size())
+      for (cudaStream_t cs : {mg->pipes[g]->copy[0], mg->pipes[g]->copy[1]})
+        if (cs && cudaStreamSynchronize(cs) != cudaSuccess && err == fastKronSuccess) err = cudaToFk(cudaGetLastError());
   }
   cudaSetDevice(cur);
   return err;
@@ -382,123 +741,150 @@ fastKronError fastKronMgGatherY(fastKronHandle handle, void* dY[], void* hY, uin
   return err;
 }
 
-// ---- per-rank form for one-process-per-GPU hosts (not part of the reference ABI) --------
-// The host program owns the ranks (e.g. torch.distributed): it passes, for every rank of
-// the column group, a pointer this process can store to (a CUDA IPC mapping), runs
-// fkbMgRankPhase1 on every rank, enqueues a collective barrier on the same stream, runs
-// fkbMgRankPhase2, and a second barrier.  `handle` must have been given its stream with
-// fastKronInitCUDA.  M is the number of local rows.
-
-fastKronError fkbMgRankPhase1(fastKronHandle handle, int rank, int world, uint32_t M, uint32_t N,
-                              uint32_t Ps[], uint32_t Qs[], const float* x, const float* const Fs[],
-                              float* temp1, float* temp2, void* const peerRecv[]) {
-  if (!handle || !Ps || !Qs || !x || !Fs || !temp1 || !temp2 || !peerRecv) return fastKronInvalidArgument;
-  Engine* e = E(handle);
-  if (!e->cudaReady()) return fastKronBackendNotAvailable;
-  MgRank r;
-  r.g = rank; r.gk = world; r.M = M; r.N = N; r.Ps = Ps; r.Qs = Qs; r.stream = e->stream(); r.smCount = e->smCount();
-  return mgPhase1(e, r, x, Fs, temp1, temp2, peerRecv);
-}
-
-// The same phase in two calls, so that a host can put an event between the local passes
-// (stage 1) and the redistributing pass (stage 2).
-fastKronError fkbMgRankPhase1Stage(fastKronHandle handle, int rank, int world, uint32_t M, uint32_t N,
-                                   uint32_t Ps[], uint32_t Qs[], const float* x, const float* const Fs[],
-                                   float* temp1, float* temp2, void* const peerRecv[], int stage) {
-  if (!handle || !Ps || !Qs || !x || !Fs || !temp1 || !temp2 || !peerRecv || stage < 1 || stage > 2)
+// ---- the same schedule for one-process-per-GPU hosts (not part of the reference ABI) ------
+// A torchrun-style host owns the ranks.  Every rank creates a pipe on its own device (the pipe
+// allocates its buffers with cudaMalloc so that they can be shared), publishes CUDA IPC handles
+// of its receive area, result block and flag array (fkbMgPipeLocalBuffers + fkbIpcExport),
+// maps its peers' (fkbIpcOpen) and hands the mapped pointers back (fkbMgPipeSetPeers).  After
+// that fkbMgPipeRun enqueues a complete product on the handle's stream: when the stream reaches
+// the end of the call this rank's result block [M][L/G] is complete.  Calls may follow one
+// another without host synchronisation; the sequence flags order them.
+//   parts   row slices (0 = choose from the block size / FASTKRON_MG_PARTS)
+//   staged  1 = copy-engine transport, 0 = peer stores from the kernels, -1 = staged when the
+//           shapes allow it
+fastKronError fkbMgPipeCreate(fastKronHandle handle, int rank, int world, uint32_t M, uint32_t N,
+                              const uint32_t Ps[], const uint32_t Qs[], int parts, int staged, void** pipeOut) {
+  if (!handle || !Ps || !Qs || !pipeOut || world < 2 || world > kMaxParts || rank < 0 || rank >= world)
     return fastKronInvalidArgument;
   Engine* e = E(handle);
   if (!e->cudaReady()) return fastKronBackendNotAvailable;
-  MgRank r;
-  r.g = rank; r.gk = world; r.M = M; r.N = N; r.Ps = Ps; r.Qs = Qs; r.stream = e->stream(); r.smCount = e->smCount();
-  return mgPhase1(e, r, x, Fs, temp1, temp2, peerRecv, stage);
-}
-
-fastKronError fkbMgRankPhase2(fastKronHandle handle, int rank, int world, uint32_t M, uint32_t N,
-                              uint32_t Ps[], uint32_t Qs[], const float* recv, const float* F0,
-                              void* const peerResult[]) {
-  if (!handle || !Ps || !Qs || !recv || !F0 || !peerResult) return fastKronInvalidArgument;
-  Engine* e = E(handle);
-  if (!e->cudaReady()) return fastKronBackendNotAvailable;
-  MgRank r;
-  r.g = rank; r.gk = world; r.M = M; r.N = N; r.Ps = Ps; r.Qs = Qs; r.stream = e->stream(); r.smCount = e->smCount();
-  return mgPhase2(e, r, recv, F0, peerResult);
-}
-
-// ---- staged form: the kernels write per-destination blocks into LOCAL staging buffers and
-// the host moves the blocks with copy engines (cudaMemcpyAsync / cudaMemcpy2DAsync to
-// IPC-mapped peer buffers), so NVLink traffic needs no SM and overlaps other rows' passes.
-// Large-factor (64/128) shapes only: the phase-2 kernel reads its input as received,
-// [sender][M][P1/G][B2].
-//   stage1: G blocks of M*(P1/G)*(Q2/G)*B elements, block d = [M][P1/G][Q2/G][B] for rank d
-//   recv  : G blocks of the same size, block s = what rank s staged for this rank
-//   stage2: G blocks of M*(Q1/G)*B2 elements, block d = [M][Q1/G][B2] for rank d, to be placed
-//           at columns [g*B2, (g+1)*B2) of rank d's [M*(Q1/G)][Q2*B] result.
-fastKronError fkbMgRankPhase1Staged(fastKronHandle handle, int rank, int world, uint32_t M, uint32_t N,
-                                    uint32_t Ps[], uint32_t Qs[], const float* x, const float* const Fs[],
-                                    float* temp1, float* temp2, float* stage1, int stage) {
-  if (!handle || !Ps || !Qs || !x || !Fs || !temp1 || !temp2 || !stage1 || stage < 0 || stage > 2)
-    return fastKronInvalidArgument;
-  Engine* e = E(handle);
-  if (!e->cudaReady()) return fastKronBackendNotAvailable;
-  MgRank r;
-  r.g = rank; r.gk = world; r.M = M; r.N = N; r.Ps = Ps; r.Qs = Qs; r.stream = e->stream(); r.smCount = e->smCount();
-  fastKronError err = mgCheck(r);
+  if (!streamMemOps().ok()) return fastKronBackendNotAvailable;
+  uint64_t K = 1;
+  for (uint32_t i = 0; i < N; i++) K *= Ps[i];
+  if (parts <= 0) parts = mgDefaultParts(M, (uint64_t)M * (K / world));
+  std::unique_ptr<MgPipe, void (*)(MgPipe*)> p(new MgPipe, mgPipeDestroy);
+  p->eng = e;
+  cudaGetDevice(&p->device);
+  p->useFlags = true;
+  fastKronError err = mgPipeGeometry(p.get(), rank, world, M, N, Ps, Qs, parts, staged);
   if (err != fastKronSuccess) return err;
-  const uint64_t p1loc = Ps[0] / world, q2loc = Qs[1] / world, B = prodQ(r, 2);
-  const uint64_t blk = (uint64_t)M * p1loc * q2loc * B;
-  void* bases[kMaxParts];
-  for (int d = 0; d < world; d++) bases[d] = stage1 + (size_t)d * blk;
-  // same kernels as the fused form; only the redistribution map differs (all bases local,
-  // rows of a block packed as [M][P1/G][Q2/G][B])
-  return mgPhase1(e, r, x, Fs, temp1, temp2, bases, stage, /*packed=*/true);
+  p->rank.smCount = e->smCount();
+  if ((err = mgPipeInitStreams(p.get())) != fastKronSuccess) return err;
+  p->owned = true;
+  const size_t tmpBytes = (size_t)p->parts * p->tmpSlice * sizeof(float);
+  const size_t recvBytes = (size_t)p->parts * p->recvSlice * sizeof(float);
+  const size_t flagBytes = (size_t)2 * p->parts * world * sizeof(uint32_t);
+  bool ok = cudaMalloc(&p->t1, tmpBytes) == cudaSuccess && cudaMalloc(&p->t2, tmpBytes) == cudaSuccess &&
+            cudaMalloc(&p->recv, recvBytes) == cudaSuccess &&
+            cudaMalloc(&p->result, (size_t)M * p->Lloc * sizeof(float)) == cudaSuccess &&
+            cudaMalloc(&p->flags, flagBytes) == cudaSuccess;
+  if (ok && p->staged) ok = cudaMalloc(&p->stage1, tmpBytes) == cudaSuccess;
+  if (!ok) { cudaGetLastError(); return fastKronOtherError; }
+  if (cudaMemset(p->flags, 0, flagBytes) != cudaSuccess) return fastKronOtherError;
+  cudaDeviceSynchronize();
+  *pipeOut = p.release();
+  return fastKronSuccess;
 }
 
-fastKronError fkbMgRankPhase2Staged(fastKronHandle handle, int rank, int world, uint32_t M, uint32_t N,
-                                    uint32_t Ps[], uint32_t Qs[], const float* recv, const float* F0,
-                                    float* stage2) {
-  if (!handle || !Ps || !Qs || !recv || !F0 || !stage2) return fastKronInvalidArgument;
-  Engine* e = E(handle);
-  if (!e->cudaReady()) return fastKronBackendNotAvailable;
-  MgRank r;
-  r.g = rank; r.gk = world; r.M = M; r.N = N; r.Ps = Ps; r.Qs = Qs; r.stream = e->stream(); r.smCount = e->smCount();
-  fastKronError err = mgCheck(r);
-  if (err != fastKronSuccess) return err;
-  const uint64_t p1loc = Ps[0] / world, q1loc = Qs[0] / world;
-  const uint64_t B2 = (Qs[1] / world) * prodQ(r, 2);
-  if (!gemmEligible(DType::F32, Ps[0], Qs[0], B2) || B2 % (uint64_t)gemmTileJ(DType::F32) != 0)
-    return fastKronKernelNotFound;
-  Pass ps;
-  ps.f0 = 0; ps.nf = 1; ps.M = M; ps.A = 1; ps.B = B2;
-  ps.P[0] = Ps[0]; ps.Q[0] = Qs[0];
-  ps.xsM = (int64_t)(Ps[0] * B2); ps.xsA = ps.xsM; ps.xsG = (int64_t)B2; ps.xsB = 1;
-  ps.zsM = (int64_t)(Qs[0] * B2); ps.zsA = ps.zsM; ps.zsG = (int64_t)B2; ps.zsB = 1;
-  ps.kind = KernelKind::Gemm;
-  LaunchCtx cx;
-  cx.stream = r.stream; cx.dt = DType::F32; cx.smCount = r.smCount; cx.tilesPerCta = e->tilesPerCta();
-  cx.src = recv; cx.dst = stage2;
-  cx.F[0] = F0;
-  factorStrides(MMType::MKM, fastKronOp_N, ps.P[0], ps.Q[0], &cx.fsP, &cx.fsQ);
-  cx.pSplit = (unsigned)p1loc; cx.pOuter = (unsigned long long)M * p1loc * B2; cx.nStride = p1loc * B2;
-  cx.scatter.parts = world; cx.scatter.qPer = q1loc; cx.scatter.aLoc = 1;
-  cx.scatter.sM = (long long)(q1loc * B2); cx.scatter.sA = 0; cx.scatter.sQ = (long long)B2; cx.scatter.zOff = 0;
-  const uint64_t blk = (uint64_t)M * q1loc * B2;
-  for (int d = 0; d < world; d++) cx.scatter.base[d] = stage2 + (size_t)d * blk;
-  // the launcher refuses the split input unless it runs the kernel: no generic fallback here
-  fastKronError le = launchGemm(ps, cx);
-  return le;
+fastKronError fkbMgPipeLocalBuffers(void* pipe, void** recv, size_t* recvBytes, void** result, size_t* resultBytes,
+                                    void** flags, size_t* flagBytes, int* parts, int* staged) {
+  MgPipe* p = reinterpret_cast<MgPipe*>(pipe);
+  if (!p) return fastKronInvalidArgument;
+  if (recv) *recv = p->recv;
+  if (recvBytes) *recvBytes = (size_t)p->parts * p->recvSlice * sizeof(float);
+  if (result) *result = p->result;
+  if (resultBytes) *resultBytes = (size_t)p->parts * p->rank.M * p->Lloc * sizeof(float);
+  if (flags) *flags = p->flags;
+  if (flagBytes) *flagBytes = (size_t)2 * p->parts * p->rank.gk * sizeof(uint32_t);
+  if (parts) *parts = p->parts;
+  if (staged) *staged = p->staged ? 1 : 0;
+  return fastKronSuccess;
 }
 
-// Stream-ordered copies for the staged form (plain cudaMemcpyAsync / cudaMemcpy2DAsync,
-// device to device; the destination may be an IPC mapping of a peer's buffer).
-int fkbCopyAsync(void* dst, const void* src, size_t bytes, void* stream) {
-  return (int)cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+// Pointers through which this process reaches every rank's receive area, result block and
+// flag array (entry `rank` = the local buffers themselves).
+fastKronError fkbMgPipeSetPeers(void* pipe, void* const recvPeers[], void* const resultPeers[],
+                                void* const flagPeers[]) {
+  MgPipe* p = reinterpret_cast<MgPipe*>(pipe);
+  if (!p || !recvPeers || !resultPeers || !flagPeers) return fastKronInvalidArgument;
+  for (int d = 0; d < p->rank.gk; d++) {
+    if (!recvPeers[d] || !resultPeers[d] || !flagPeers[d]) return fastKronInvalidArgument;
+    p->recvPeer[d] = recvPeers[d];
+    p->resultPeer[d] = resultPeers[d];
+    p->flagPeer[d] = reinterpret_cast<uint32_t*>(flagPeers[d]);
+  }
+  if (p->recvPeer[p->rank.g] != p->recv || p->resultPeer[p->rank.g] != p->result) return fastKronInvalidArgument;
+  p->peersSet = true;
+  return fastKronSuccess;
 }
-int fkbCopy2DAsync(void* dst, size_t dpitch, const void* src, size_t spitch, size_t widthBytes, size_t height,
-                   void* stream) {
-  return (int)cudaMemcpy2DAsync(dst, dpitch, src, spitch, widthBytes, height, cudaMemcpyDeviceToDevice,
-                                (cudaStream_t)stream);
+
+// x: this rank's [M][K/G] block on the device; Fs: host array of N device pointers.  With
+// hostX / hostZ (pinned host memory, [M][K/G] and [M][L/G], contiguous) the call also moves
+// the operands: every slice is copied in before its first pass and copied out as soon as it
+// is complete, on side streams, so the copies of one slice overlap the passes of the others.
+static fastKronError mgPipeRun(MgPipe* p, const float* x, const float* const Fs[], const float* hostX, float* hostZ) {
+  if (!p || !Fs || !p->peersSet || (!x && !hostX)) return fastKronInvalidArgument;
+  Engine* e = p->eng;
+  p->compute = e->stream();
+  p->seq++;
+  const uint32_t Mi = p->rank.M;
+  fastKronError err = fastKronSuccess;
+  if (hostX) {
+    if (!p->xdev && cudaMalloc(&p->xdev, (size_t)p->parts * Mi * p->Kloc * sizeof(float)) != cudaSuccess) {
+      cudaGetLastError();
+      return fastKronOtherError;
+    }
+    x = p->xdev;
+    // the device copy of X may only be overwritten once the previous call has finished with it
+    cudaEvent_t tail = p->evIn[0];
+    if (cudaEventRecord(tail, p->compute) != cudaSuccess || cudaStreamWaitEvent(p->h2d, tail, 0) != cudaSuccess)
+      return fastKronOtherError;
+    for (int s = 0; s < p->parts; s++) {
+      const size_t off = (size_t)s * Mi * p->Kloc;
+      if (cudaMemcpyAsync(p->xdev + off, hostX + off, (size_t)Mi * p->Kloc * sizeof(float), cudaMemcpyHostToDevice,
+                          p->h2d) != cudaSuccess ||
+          cudaEventRecord(p->evIn[s], p->h2d) != cudaSuccess)
+        return fastKronOtherError;
+    }
+  }
+  std::vector<std::pair<int, int>> order;
+  mgOrder(p->parts, &order);
+  for (size_t o = 0; o < order.size() && err == fastKronSuccess; o++) {
+    const int s = order[o].second;
+    if (order[o].first == 1) {
+      if (hostX && cudaStreamWaitEvent(p->compute, p->evIn[s], 0) != cudaSuccess) return fastKronOtherError;
+      err = mgEnqueueP1(p, s, x, Fs);
+    } else {
+      err = mgEnqueueP2(p, s, Fs[0]);
+      if (err == fastKronSuccess && hostZ) {
+        // slice s of the result leaves as soon as every rank's rows of it have landed
+        err = mgWaitResult(p, s, p->d2h);
+        const size_t off = (size_t)s * Mi * p->Lloc;
+        if (err == fastKronSuccess &&
+            cudaMemcpyAsync(hostZ + off, p->result + off, (size_t)Mi * p->Lloc * sizeof(float), cudaMemcpyDeviceToHost,
+                            p->d2h) != cudaSuccess)
+          err = fastKronOtherError;
+      }
+    }
+  }
+  for (int s = 0; s < p->parts && err == fastKronSuccess; s++) err = mgWaitResult(p, s, p->compute);
+  if (err == fastKronSuccess && hostZ) {
+    cudaEvent_t done = p->evC3[0];       // free again: every use of it in this call is enqueued
+    if (cudaEventRecord(done, p->d2h) != cudaSuccess || cudaStreamWaitEvent(p->compute, done, 0) != cudaSuccess)
+      err = fastKronOtherError;
+  }
+  return err;
 }
+
+fastKronError fkbMgPipeRun(void* pipe, const float* x, const float* const Fs[]) {
+  return mgPipeRun(reinterpret_cast<MgPipe*>(pipe), x, Fs, nullptr, nullptr);
+}
+fastKronError fkbMgPipeRunHost(void* pipe, const float* hostX, const float* const Fs[], float* hostZ) {
+  if (!hostX || !hostZ) return fastKronInvalidArgument;
+  return mgPipeRun(reinterpret_cast<MgPipe*>(pipe), nullptr, Fs, hostX, hostZ);
+}
+
+void fkbMgPipeDestroy(void* pipe) { mgPipeDestroy(reinterpret_cast<MgPipe*>(pipe)); }
 
 // The two redistribution maps as plain numbers, for host-side (CPU) tests of the schedule:
 // out[0..6] = parts, qPer, aLoc, sM, sA, sQ, zOff.
@@ -516,9 +902,17 @@ fastKronError fkbMgScatterDesc(int phase, int rank, int world, uint32_t N, const
   return fastKronSuccess;
 }
 
+// The enqueue order of a call with `parts` row slices as (half, slice) pairs, for the CPU
+// tests of the schedule: out[2*i] = 1 (first half) or 2 (second half), out[2*i+1] = slice.
+int fkbMgOrder(int parts, int out[], int maxPairs) {
+  std::vector<std::pair<int, int>> order;
+  mgOrder(parts < 1 ? 1 : parts, &order);
+  int n = 0;
+  for (; n < (int)order.size() && n < maxPairs; n++) { out[2 * n] = order[n].first; out[2 * n + 1] = order[n].second; }
+  return (int)order.size();
+}
+
 // CUDA IPC helpers so that a Python host can exchange buffer handles between ranks.
-int fkbIpcAlloc(void** ptr, size_t bytes) { return (int)cudaMalloc(ptr, bytes); }
-int fkbIpcFree(void* ptr) { return (int)cudaFree(ptr); }
 int fkbIpcExport(void* ptr, unsigned char handleOut[64]) {
   cudaIpcMemHandle_t h;
   const cudaError_t e = cudaIpcGetMemHandle(&h, ptr);

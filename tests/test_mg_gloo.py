@@ -112,3 +112,24 @@ def test_scatter_desc_rejects_bad_grids():
         mg.scatter_desc(1, 0, 4, [6, 4], [4, 4])         # 4 does not divide P1
     d = mg.scatter_desc(2, 1, 2, [4, 4, 4], [4, 4, 4])
     assert d["parts"] == 2 and d["qPer"] == 2 and d["sQ"] == 16 and d["zOff"] == 8
+
+
+def test_schedule_order_of_row_slices():
+    """Host logic of the pipelined schedule: with R row slices a call enqueues, on a GPU's one
+    compute stream, P1(0), P1(1), P2(0), ..., P2(R-1): every slice's second half comes after its
+    first half and after the NEXT slice's first half (whose passes hide this slice's transfer)."""
+    import ctypes
+    from fastkron_b200 import lib as fk
+    L = fk.get()
+    for R in (1, 2, 3, 4, 8):
+        out = (ctypes.c_int * (4 * R))()
+        n = L.fkbMgOrder(ctypes.c_int(R), out, ctypes.c_int(2 * R))
+        assert n == 2 * R
+        seq = [(out[2 * i], out[2 * i + 1]) for i in range(n)]
+        assert sorted(seq) == sorted([(1, s) for s in range(R)] + [(2, s) for s in range(R)])
+        pos = {hs: i for i, hs in enumerate(seq)}
+        for s in range(R):
+            assert pos[(1, s)] < pos[(2, s)]
+            if s + 1 < R:
+                assert pos[(1, s + 1)] < pos[(2, s)]
+                assert pos[(2, s)] < pos[(2, s + 1)]

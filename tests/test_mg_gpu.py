@@ -35,11 +35,20 @@ MG_CASES = [
 ]
 
 
+def _cuda_free(ptr):
+    """cudaFree through the CUDA runtime torch has loaded (fastKronMgAllocX hands out cudaMalloc blocks)."""
+    rt = ctypes.CDLL("libcudart.so.12")
+    rt.cudaFree.argtypes = [ctypes.c_void_p]
+    return rt.cudaFree(ctypes.c_void_p(ptr))
+
+
+@pytest.mark.parametrize("parts", [1, 2])
 @pytest.mark.parametrize("M,ps,qs,GM,GK", MG_CASES, ids=lambda v: str(v).replace(" ", ""))
-def test_mg_api_on_logical_gpus(M, ps, qs, GM, GK, monkeypatch):
+def test_mg_api_on_logical_gpus(M, ps, qs, GM, GK, parts, monkeypatch):
     import torch
     from fastkron_b200 import lib as fk
     monkeypatch.setenv("FASTKRON_MG_ONE_DEVICE", "1")
+    monkeypatch.setenv("FASTKRON_MG_PARTS", str(parts))     # row slices of the pipelined schedule
     L = fk.get()
     gpus = GM * GK
     n = len(ps)
@@ -77,10 +86,11 @@ def test_mg_api_on_logical_gpus(M, ps, qs, GM, GK, monkeypatch):
     assert L.fastKronMgGatherY(h, P(res), ctypes.c_void_p(zh.ctypes.data), ctypes.c_uint32(M), ctypes.c_uint32(K),
                                ctypes.c_uint32(n), fk.u32arr(qs), fk.u32arr(ps)) == fk.SUCCESS
     assert cases.row_rel_err(zh, want, "mkm") <= cases.TOL["f32"]
-    # X blocks were allocated by the library with cudaMalloc; the caller frees them
-    cudart = ctypes.CDLL("libcudart.so") if False else None
-    _ = cudart
     L.fastKronDestroy(h)
+    # X blocks were allocated by the library with cudaMalloc; the caller frees them
+    torch.cuda.synchronize()
+    for g in range(gpus):
+        assert _cuda_free(dX[g]) == 0
 
 
 def test_mg_init_argument_errors():
