@@ -149,6 +149,17 @@ def run(args, CONFIGS, B):
                 tt.append(float(t.item()))
         single_ms = float(np.mean(tt))
 
+        # ---- where a step's time goes: CUDA events around every kernel of one extra step ----
+        L.fkbSetProfiling(eng.h.h, 1)
+        eng.run(x, fs)
+        torch.cuda.synchronize()
+        pm = (ctypes.c_float * 4096)()
+        pk = (ctypes.c_int * 4096)()
+        npass = L.fkbGetPassTimes(eng.h.h, pm, pk, 4096)
+        L.fkbSetProfiling(eng.h.h, 0)
+        kernel_ms = [float(pm[i]) for i in range(npass)]
+        dist.barrier()
+
         # ---- end to end: host block -> device, product, device -> host, every step ---------
         hx = torch.empty(M * Kl, dtype=torch.float32, pin_memory=True)
         hz = torch.empty(M * Ll, dtype=torch.float32, pin_memory=True)
@@ -186,7 +197,32 @@ def run(args, CONFIGS, B):
             if it > 0:
                 copy_tt.append(float(t.item()))
         h2d_alone_ms = float(np.mean(copy_tt))
-        del xd2
+        # both directions at once, all ranks at once: the ceiling of any end-to-end schedule
+        zd2 = torch.empty(M * Ll, dtype=torch.float32, device="cuda")
+        s_a, s_b = torch.cuda.Stream(), torch.cuda.Stream()
+        copy_tt = []
+        for it in range(3):
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            s_a.wait_stream(stream)
+            s_b.wait_stream(stream)
+            with torch.cuda.stream(s_a):
+                xd2.copy_(hx, non_blocking=True)
+            with torch.cuda.stream(s_b):
+                hz.copy_(zd2, non_blocking=True)
+            stream.wait_stream(s_a)
+            stream.wait_stream(s_b)
+            b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b)], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if it > 0:
+                copy_tt.append(float(t.item()))
+        duplex_alone_ms = float(np.mean(copy_tt))
+        del xd2, zd2
 
         # ---- parity spot check outside the timed region: two full rows against the oracle ----
         z = eng.run(x, fs).clone()
@@ -249,12 +285,16 @@ def run(args, CONFIGS, B):
             "value_harness_count": B["flops_harness"](c) / (ms_step * 1e-3) / 1e9,
             "gpu_launches": launches * world, "clocks": clocks, "roofline": roof,
             "single_call_ms": single_ms,
+            "kernel_ms_one_step_rank0": {"sum": float(np.sum(kernel_ms)), "count": len(kernel_ms),
+                                         "each": [round(v, 3) for v in kernel_ms[:64]]},
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
                     "h2d_bytes_per_step": M * Kl * 4 * world, "d2h_bytes_per_step": M * Ll * 4 * world,
                     "ms_per_step": e2e_ms, "steps": e2e_steps, "row_slices": parts,
                     "how": "each rank's pinned block: a row slice is copied in ahead of its passes and copied out when complete",
                     "h2d_alone_ms_all_ranks": h2d_alone_ms,
                     "h2d_alone_gbs_aggregate": M * Kl * 4 * world / (h2d_alone_ms * 1e-3) / 1e9,
+                    "copies_alone_both_directions_ms_all_ranks": duplex_alone_ms,
+                    "copies_alone_gbs_aggregate_per_direction": M * Kl * 4 * world / (duplex_alone_ms * 1e-3) / 1e9,
                     "matches_device_result": e2e_same},
             "cpu_baseline": None, "parity_rows_max_rel_err": check,
             "row_slices": parts, "exchange_mode": mode, "c_api_single_process": c_api,

@@ -262,8 +262,13 @@ struct MgPipe {
   uint32_t* flagPeer[kMaxParts] = {nullptr};
   bool peersSet = false;
   cudaStream_t compute = nullptr;
-  cudaStream_t copy[2] = {nullptr, nullptr};
+  // side streams of the transport: a slice's copies are spread over them by destination, so
+  // several copy engines (and NVLink paths to different peers) work at once
+  static constexpr int NC = 4;
+  cudaStream_t copy[NC] = {nullptr, nullptr, nullptr, nullptr};
   cudaStream_t h2d = nullptr, d2h = nullptr;
+  // per slice: passes done (evC2, evC3), host block arrived (evIn); per slice and side stream:
+  // this rank's outgoing copies of exchange 1 / 2 done (evX1, evX2)
   std::vector<cudaEvent_t> evC2, evC3, evX1, evX2, evIn;
   uint32_t seq = 0;
   MgPipe* const* group = nullptr;         // one process: the pipes of this row group, by column rank
@@ -278,7 +283,9 @@ static void mgPipeDestroy(MgPipe* p) {
   cudaSetDevice(p->device);
   for (auto* v : {&p->evC2, &p->evC3, &p->evX1, &p->evX2, &p->evIn})
     for (cudaEvent_t e : *v) cudaEventDestroy(e);
-  for (cudaStream_t s : {p->copy[0], p->copy[1], p->h2d, p->d2h})
+  for (cudaStream_t s : p->copy)
+    if (s) cudaStreamDestroy(s);
+  for (cudaStream_t s : {p->h2d, p->d2h})
     if (s) cudaStreamDestroy(s);
   if (p->owned) {
     for (float* b : {p->t1, p->t2, p->stage1, p->recv, p->result, p->xdev})
@@ -293,12 +300,13 @@ static void mgPipeDestroy(MgPipe* p) {
 static fastKronError mgPipeInitStreams(MgPipe* p) {
   int lo = 0, hi = 0;
   cudaDeviceGetStreamPriorityRange(&lo, &hi);
-  for (int i = 0; i < 2; i++)
+  for (int i = 0; i < MgPipe::NC; i++)
     if (cudaStreamCreateWithPriority(&p->copy[i], cudaStreamNonBlocking, hi) != cudaSuccess) return fastKronOtherError;
   if (cudaStreamCreateWithPriority(&p->h2d, cudaStreamNonBlocking, hi) != cudaSuccess) return fastKronOtherError;
   if (cudaStreamCreateWithPriority(&p->d2h, cudaStreamNonBlocking, hi) != cudaSuccess) return fastKronOtherError;
   for (auto* v : {&p->evC2, &p->evC3, &p->evX1, &p->evX2, &p->evIn}) {
-    for (int s = 0; s < p->parts; s++) {
+    const int n = (v == &p->evX1 || v == &p->evX2) ? p->parts * MgPipe::NC : p->parts;
+    for (int s = 0; s < n; s++) {
       cudaEvent_t ev;
       if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return fastKronOtherError;
       v->push_back(ev);
@@ -324,8 +332,19 @@ static fastKronError mgPipeGeometry(MgPipe* p, int g, int gk, uint32_t rows, uin
   p->parts = parts;
   p->rank.M = rows / parts;
   const bool can = mgStagedEligible(p->rank);
+  // FASTKRON_MG_MODE=fused|staged overrides the automatic choice (a supported knob)
+  if (wantStaged < 0) {
+    const char* m = getenv("FASTKRON_MG_MODE");
+    if (m && !strcmp(m, "fused")) wantStaged = 0;
+    else if (m && !strcmp(m, "staged") && can) wantStaged = 1;
+  }
   if (wantStaged == 1 && !can) return fastKronKernelNotFound;
-  p->staged = wantStaged == 0 ? false : can;
+  // Automatic choice, from measurements on 8 B200 behind NVSwitch: with two GPUs half of every
+  // block stays local and storing straight from the kernels wins (C5: 26.3 ms against 28.6 ms);
+  // from four GPUs on, the copy engines win because the kernels then run at full speed while
+  // the NVLink traffic of another row slice is in flight.
+  if (wantStaged < 0) wantStaged = (can && gk >= 3) ? 1 : 0;
+  p->staged = wantStaged == 1;
   const uint64_t B = prodQ(p->rank, 2);
   const uint64_t p1loc = Ps[0] / gk, q1loc = Qs[0] / gk, q2loc = Qs[1] / gk;
   p->B2 = q2loc * B;
@@ -342,11 +361,23 @@ static fastKronError mgPipeGeometry(MgPipe* p, int g, int gk, uint32_t rows, uin
 }
 
 // ---- ordering primitives --------------------------------------------------------------------
-// signal(phase, slice) on `s`: this rank's outgoing blocks of that slice and phase have landed.
-// With flags, the signal towards rank d is written right after the copy to d (see the copies).
-static fastKronError mgSignalAll(MgPipe* p, int phase, int slice, cudaStream_t s) {
+// A slice's outgoing copies of one exchange run on the NC side streams (fused transport: there
+// are none, the kernel itself stored the rows and "side stream" means the compute stream).
+// mgSignal records, per side stream, that this rank's copies of (phase, slice) on it are done;
+// with flags, the message towards rank d is written right after the copy to d instead.
+static fastKronError mgSignal(MgPipe* p, int phase, int slice) {
   std::vector<cudaEvent_t>& ev = phase == 0 ? p->evX1 : p->evX2;
-  if (cudaEventRecord(ev[slice], s) != cudaSuccess) return fastKronOtherError;
+  for (int c = 0; c < MgPipe::NC; c++) {
+    cudaStream_t s = p->staged ? p->copy[c] : p->compute;
+    if (cudaEventRecord(ev[(size_t)slice * MgPipe::NC + c], s) != cudaSuccess) return fastKronOtherError;
+    if (!p->staged) break;                 // one stream only: event 0 stands for the slice
+  }
+  return fastKronSuccess;
+}
+static fastKronError mgWaitEvents(MgPipe* q, int phase, int slice, cudaStream_t s) {
+  const std::vector<cudaEvent_t>& ev = phase == 0 ? q->evX1 : q->evX2;
+  for (int c = 0; c < (q->staged ? MgPipe::NC : 1); c++)
+    if (cudaStreamWaitEvent(s, ev[(size_t)slice * MgPipe::NC + c], 0) != cudaSuccess) return fastKronOtherError;
   return fastKronSuccess;
 }
 static fastKronError mgFlagTo(MgPipe* p, int phase, int slice, int d, cudaStream_t s) {
@@ -370,9 +401,8 @@ static fastKronError mgWaitAll(MgPipe* p, int phase, int slice, cudaStream_t s) 
   }
   for (int d = 0; d < G; d++) {
     if (d == g) continue;
-    MgPipe* q = p->group[d];
-    cudaEvent_t ev = phase == 0 ? q->evX1[slice] : q->evX2[slice];
-    if (cudaStreamWaitEvent(s, ev, 0) != cudaSuccess) return fastKronOtherError;
+    fastKronError err = mgWaitEvents(p->group[d], phase, slice, s);
+    if (err != fastKronSuccess) return err;
   }
   return fastKronSuccess;
 }
@@ -398,11 +428,12 @@ static fastKronError mgEnqueueP1(MgPipe* p, int s, const float* x, const float* 
   fastKronError err = mgPhase1(p->eng, r, xs, Fs, t1, t2, bases, p->staged);
   if (err != fastKronSuccess) return err;
   if (cudaEventRecord(p->evC2[s], p->compute) != cudaSuccess) return fastKronOtherError;
-  cudaStream_t cs = p->staged ? p->copy[s & 1] : p->compute;
   if (p->staged) {
-    if (cudaStreamWaitEvent(cs, p->evC2[s], 0) != cudaSuccess) return fastKronOtherError;
+    for (int c = 0; c < MgPipe::NC; c++)
+      if (cudaStreamWaitEvent(p->copy[c], p->evC2[s], 0) != cudaSuccess) return fastKronOtherError;
     for (int k = 1; k < G; k++) {
       const int d = (g + k) % G;
+      cudaStream_t cs = p->copy[(k + s) % MgPipe::NC];
       float* dst = (float*)p->recvPeer[d] + (size_t)s * p->recvSlice + (size_t)g * p->blk1;
       if (cudaMemcpyAsync(dst, bases[d], p->blk1 * sizeof(float), cudaMemcpyDeviceToDevice, cs) != cudaSuccess)
         return fastKronOtherError;
@@ -410,9 +441,9 @@ static fastKronError mgEnqueueP1(MgPipe* p, int s, const float* x, const float* 
     }
   } else {
     for (int k = 1; k < G; k++)
-      if ((err = mgFlagTo(p, 0, s, (g + k) % G, cs)) != fastKronSuccess) return err;
+      if ((err = mgFlagTo(p, 0, s, (g + k) % G, p->compute)) != fastKronSuccess) return err;
   }
-  return mgSignalAll(p, 0, s, cs);
+  return mgSignal(p, 0, s);
 }
 
 static fastKronError mgEnqueueP2(MgPipe* p, int s, const float* F0) {
@@ -424,16 +455,17 @@ static fastKronError mgEnqueueP2(MgPipe* p, int s, const float* F0) {
   const float* recvS = (const float*)p->recvPeer[g] + (size_t)s * p->recvSlice;
   const uint64_t q1loc = p->Qs[0] / G;
   const size_t resSlice = (size_t)s * r.M * p->Lloc;            // rows of this slice in a result block
-  cudaStream_t cs = p->staged ? p->copy[s & 1] : p->compute;
   if (p->staged) {
     float* st2 = p->t1 + (size_t)s * p->tmpSlice;               // free again: every local pass of the slice is done
     err = mgPhase2Staged(p->eng, r, recvS, F0, st2);
     if (err != fastKronSuccess) return err;
     if (cudaEventRecord(p->evC3[s], p->compute) != cudaSuccess) return fastKronOtherError;
-    if (cudaStreamWaitEvent(cs, p->evC3[s], 0) != cudaSuccess) return fastKronOtherError;
+    for (int c = 0; c < MgPipe::NC; c++)
+      if (cudaStreamWaitEvent(p->copy[c], p->evC3[s], 0) != cudaSuccess) return fastKronOtherError;
     const size_t rows = (size_t)r.M * q1loc, width = p->B2 * sizeof(float), dpitch = (size_t)G * width;
     for (int k = 0; k < G; k++) {
       const int d = (g + k) % G;
+      cudaStream_t cs = p->copy[(k + s) % MgPipe::NC];
       float* dst = (float*)p->resultPeer[d] + resSlice + (size_t)g * p->B2;
       if (cudaMemcpy2DAsync(dst, dpitch, st2 + (size_t)d * p->blk2, width, width, rows, cudaMemcpyDeviceToDevice,
                             cs) != cudaSuccess)
@@ -446,15 +478,16 @@ static fastKronError mgEnqueueP2(MgPipe* p, int s, const float* F0) {
     err = mgPhase2(p->eng, r, recvS, F0, res);
     if (err != fastKronSuccess) return err;
     for (int k = 1; k < G; k++)
-      if ((err = mgFlagTo(p, 1, s, (g + k) % G, cs)) != fastKronSuccess) return err;
+      if ((err = mgFlagTo(p, 1, s, (g + k) % G, p->compute)) != fastKronSuccess) return err;
   }
-  return mgSignalAll(p, 1, s, cs);
+  return mgSignal(p, 1, s);
 }
 
 // `stream` waits until slice s of this rank's result block is complete: its own outgoing
 // copies are done and every peer's rows have arrived.
 static fastKronError mgWaitResult(MgPipe* p, int s, cudaStream_t stream) {
-  if (cudaStreamWaitEvent(stream, p->evX2[s], 0) != cudaSuccess) return fastKronOtherError;
+  fastKronError err = mgWaitEvents(p, 1, s, stream);
+  if (err != fastKronSuccess) return err;
   return mgWaitAll(p, 1, s, stream);
 }
 
@@ -685,7 +718,7 @@ fastKronError fastKronMgSGEMM(fastKronHandle handle, const uint32_t NumKronMats,
     cudaSetDevice(mg->device[g]);
     if (cudaStreamSynchronize(streamOf(g)) != cudaSuccess && err == fastKronSuccess) err = cudaToFk(cudaGetLastError());
     if (g < (int)mg->pipes.size())
-      for (cudaStream_t cs : {mg->pipes[g]->copy[0], mg->pipes[g]->copy[1]})
+      for (cudaStream_t cs : mg->pipes[g]->copy)
         if (cs && cudaStreamSynchronize(cs) != cudaSuccess && err == fastKronSuccess) err = cudaToFk(cudaGetLastError());
   }
   cudaSetDevice(cur);
