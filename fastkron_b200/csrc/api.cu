@@ -269,6 +269,10 @@ int fkbGetPassTimes(fastKronHandle handle, float* ms, int* kinds, int maxN) {
   return E(handle)->passTimes(ms, kinds, maxN);
 }
 
+// Tuner hook (fastkron_b200/tune.py): cap the fusion depth of every plan made afterwards by
+// this process (0 = none).  Cached plans of existing handles are not revisited.
+void fkbSetMaxFuse(int cap) { setMaxFuseOverride(cap); }
+
 // ---- introspection used by the host-side tests (not part of the reference ABI) --
 // Writes the textual plan of a problem into buf; returns the number of passes
 // or a negative fastKronError.

@@ -19,17 +19,17 @@
 
 using namespace fkb;
 
-template <typename T, int P, int NF, int BT, int J>
+template <typename T, int P, int NF, int BT, int J, bool SWZ>
 struct HostChain {
   static void run(T* tile, const T* Fs, int E) {
     constexpr int S = ipow(P, NF - 1 - J) * BT;
     for (int tid = 0; tid < kTileThreads; tid++)
-      stepDispatch<T, P, S, kTileThreads>(tile, Fs + J * P * P, E, tid);
-    HostChain<T, P, NF, BT, J - 1>::run(tile, Fs, E);
+      stepDispatch<T, P, S, kTileThreads, SWZ>(tile, Fs + J * P * P, E, tid);
+    HostChain<T, P, NF, BT, J - 1, SWZ>::run(tile, Fs, E);
   }
 };
-template <typename T, int P, int NF, int BT>
-struct HostChain<T, P, NF, BT, -1> {
+template <typename T, int P, int NF, int BT, bool SWZ>
+struct HostChain<T, P, NF, BT, -1, SWZ> {
   static void run(T*, const T*, int) {}
 };
 
@@ -38,7 +38,8 @@ static double urand(unsigned long long& s) {
   return (double)((s >> 11) & ((1ull << 53) - 1)) / 9007199254740992.0 * 2.0 - 1.0;
 }
 
-template <typename T, int P, int NF, bool WIDE>
+// SWZ = false: the linear tile layout of the TMA-staged kernels (wide fp32 only).
+template <typename T, int P, int NF, bool WIDE, bool SWZ = true>
 static int runOne(int R, unsigned long long chunks, unsigned long long Bmul) {
   constexpr int VEC = Vec16<T>::N;
   constexpr int BT = WIDE ? (int)(128 / sizeof(T)) : 1;
@@ -67,15 +68,15 @@ static int runOne(int R, unsigned long long chunks, unsigned long long Bmul) {
     for (int v = 0; v < nvec; v++) {
       const unsigned idx = (unsigned)v * VEC;
       const unsigned long long goff = tileGlobalOffset<WIDE, SUB, BT>(bases.data(), st0 * G, idx, B);
-      const unsigned ph = physIdx<T>(idx);
+      const unsigned ph = physIdx<T, SWZ>(idx);
       for (int i = 0; i < VEC; i++) { tile[ph + i] = X[goff + i]; written[ph + i]++; }
     }
     for (int i = 0; i < E; i++) if (written[i] != 1) { printf("swizzle is not a permutation\n"); return 1; }
-    HostChain<T, P, NF, BT, NF - 1>::run(tile.data(), Fs.data(), E);
+    HostChain<T, P, NF, BT, NF - 1, SWZ>::run(tile.data(), Fs.data(), E);
     for (int v = 0; v < nvec; v++) {
       const unsigned idx = (unsigned)v * VEC;
       const unsigned long long goff = tileGlobalOffset<WIDE, SUB, BT>(bases.data(), st0 * G, idx, B);
-      const unsigned ph = physIdx<T>(idx);
+      const unsigned ph = physIdx<T, SWZ>(idx);
       for (int i = 0; i < VEC; i++) Z[goff + i] = tile[ph + i];
     }
   }
@@ -101,8 +102,8 @@ static int runOne(int R, unsigned long long chunks, unsigned long long Bmul) {
   }
   const double tol = (sizeof(T) == 4 ? 2e-5 : 1e-13) * (maxRef > 1 ? maxRef : 1);
   const bool ok = maxErr <= tol;
-  printf("%s P=%-2d NF=%d %s R=%-2d chunks=%llu B=%llu  maxErr=%.3g (ref %.3g)  %s\n",
-         sizeof(T) == 4 ? "f32" : "f64", P, NF, WIDE ? "wide  " : "narrow", R, chunks, B, maxErr, maxRef,
+  printf("%s P=%-2d NF=%d %s%s R=%-2d chunks=%llu B=%llu  maxErr=%.3g (ref %.3g)  %s\n",
+         sizeof(T) == 4 ? "f32" : "f64", P, NF, WIDE ? "wide  " : "narrow", SWZ ? "" : " linear", R, chunks, B, maxErr, maxRef,
          ok ? "ok" : "MISMATCH");
   return ok ? 0 : 1;
 }
@@ -112,7 +113,8 @@ static int runAll() {
   int bad = 0;
   // R = 3 exercises several sub-tiles per super-tile and a ragged last super-tile.
 #define EMU_N(p, n) if ((size_t)ipow(p, n) * sizeof(T) >= 16) { bad += runOne<T, p, n, false>(3, 7, 1); bad += runOne<T, p, n, false>(1, 2, 1); }
-#define EMU_W(p, n) bad += runOne<T, p, n, true>(3, 2, 2); bad += runOne<T, p, n, true>(1, 1, 1);
+#define EMU_W(p, n) bad += runOne<T, p, n, true>(3, 2, 2); bad += runOne<T, p, n, true>(1, 1, 1); \
+  if (sizeof(T) == 4) bad += runOne<T, p, n, true, false>(3, 2, 2);
   FKB_TILE_NARROW(EMU_N)
   FKB_TILE_WIDE(EMU_W)
 #undef EMU_N

@@ -168,17 +168,29 @@ fastKronError Engine::run(Problem pr, const CallOperands& ops) {
     Plan plan;
     fastKronError e = makePlan(pr, po, &plan);
     if (e != fastKronSuccess) return e;
-    // fastKronOptionsTune: time the candidate plans once on the caller's own buffers (X and
-    // the factors are never written; Z and the temporaries are scratch until the real run)
-    // and keep the fastest.  Skipped when Z aliases Y, whose contents the trial runs would
-    // destroy.  (Role of the reference's Autotuner::tune, src/autotuner/autotuner.cpp:24-328.)
+    // fastKronOptionsTune: time candidate plans once on the caller's own buffers (X and the
+    // factors are never written; Z and the temporaries are scratch until the real run) and keep
+    // the fastest.  Candidates: the table's plan, the unfused plan, and every distinct plan that
+    // a cap on the fusion depth produces (4+4, 3+3+2, 2+2+2+2, ...).  Skipped when Z aliases Y,
+    // whose contents the trial runs would destroy.  (Role of the reference's Autotuner::tune,
+    // src/autotuner/autotuner.cpp:24-328, with the candidates reduced to what differs here: the
+    // kernels' own parameters are tuned offline, fastkron_b200/tune.py.)
     if ((options_ & fastKronOptionsTune) != 0 && pr.batch == 1 && (const void*)ops.Z != ops.Y) {
-      PlanOptions alt = po;
-      alt.fusion = !po.fusion;
-      Plan other;
-      if (makePlan(pr, alt, &other) == fastKronSuccess && other.passes.size() != plan.passes.size()) {
-        const float tA = timePlan(pr, plan, ops), tB = timePlan(pr, other, ops);
-        if (tB > 0.f && tA > 0.f && tB < tA) plan = other;
+      std::vector<std::string> seen{plan.describe()};
+      float best = timePlan(pr, plan, ops);
+      for (int cap = 1; cap <= kMaxGroup && best > 0.f; cap++) {
+        PlanOptions alt = po;
+        alt.fusion = true;
+        alt.maxFuse = cap;
+        Plan other;
+        if (makePlan(pr, alt, &other) != fastKronSuccess) continue;
+        const std::string d = other.describe();
+        bool dup = false;
+        for (const std::string& s2 : seen) dup = dup || s2 == d;
+        if (dup) continue;
+        seen.push_back(d);
+        const float t = timePlan(pr, other, ops);
+        if (t > 0.f && t < best) { best = t; plan = other; }
       }
     }
     // FASTKRON_LOG=INFO (or DEBUG): one block per newly planned problem, as the reference prints

@@ -77,7 +77,7 @@ struct Pass {
   bool     epilogue = false;    // apply alpha / beta*Y (Y laid out like the output)
   // tuning knobs chosen by the planner for Tile / Gemm kernels
   int      tileB = 1;           // trailing-dimension elements per tile
-  int      tileR = 1;           // consecutive (m,a) chunks per tile when B == 1
+  int      tileR = 0;           // Tile kernels: super-tile size in KB (0 = the launcher's default)
   int      variant = 0;         // kernel-specific variant id
   uint64_t Pg() const { uint64_t g = 1; for (int i = 0; i < nf; i++) g *= P[i]; return g; }
   uint64_t Qg() const { uint64_t g = 1; for (int i = 0; i < nf; i++) g *= Q[i]; return g; }
@@ -94,6 +94,7 @@ struct PlanOptions {
   bool haveT2 = true;           // caller supplied temp2
   bool forceGeneric = false;    // debugging / parity cross-check
   bool isolateFirst = false;    // factor 0 gets a pass of its own (multi-GPU: that pass redistributes)
+  int  maxFuse = 0;             // cap on the factors one tile pass fuses (0 = none); fastKronOptionsTune sweeps it
   size_t smemBudget = 200 * 1024;
   // pointer alignment of X / Z / temps in bytes (vector kernels need 16)
   int  align = 16;
@@ -101,5 +102,7 @@ struct PlanOptions {
 
 // Build the list of passes for a problem.  Pure host code.
 fastKronError makePlan(const Problem& pr, const PlanOptions& opt, Plan* out);
+// Process-wide cap on the fusion depth (the offline tuner's hook; 0 = none).
+void setMaxFuseOverride(int cap);
 
 }  // namespace fkb

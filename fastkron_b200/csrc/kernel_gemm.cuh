@@ -183,7 +183,10 @@ struct AccBlock<float, MQ, MJ, true, true> {
   }
 };
 
-template <typename T, int P, int Q, int TJ, int PC, int STAGES, int MQ, int MJ, bool XT, int UNR = 8, int MINB = 0, bool PACK = false>
+// ABL (the tuning tool only; always 0 in the library): timing ablations that produce wrong
+// results on purpose -- bit 0 drops the global stores, bit 1 the stage loads after the first
+// ring fill, bit 2 the CTA barrier of the stage loop.
+template <typename T, int P, int Q, int TJ, int PC, int STAGES, int MQ, int MJ, bool XT, int UNR = 8, int MINB = 0, bool PACK = false, int ABL = 0>
 __global__ void __launch_bounds__((Q / MQ) * (TJ / MJ), (MINB > 0 ? MINB : ((Q / MQ) * (TJ / MJ) <= 256 ? 2 : 1)))
 gemmPassKernel(const GemmArgs<T> a, const __grid_constant__ CUtensorMap tmap) {
   using C = GemmCfg<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT>;
@@ -315,14 +318,14 @@ gemmPassKernel(const GemmArgs<T> a, const __grid_constant__ CUtensorMap tmap) {
   unsigned slot = 0;
   unsigned phases = 0;                 // bit i: parity of the next completion of fullBar[i]
   for (unsigned s = 0; s < total; s++) {
-    if (tma) {
+    if (tma && !(ABL & 2)) {
       if (!mbarWaitBounded(&fullBar[slot], (phases >> slot) & 1u)) return;
       phases ^= 1u << slot;
     } else {
       cpAsyncWait<STAGES - 2>();
     }
-    __syncthreads();
-    if (s + STAGES - 1 < total) issue();
+    if (!(ABL & 4)) __syncthreads();
+    if (s + STAGES - 1 < total && !(ABL & 2)) issue();
     cpAsyncCommit();
 
     const T* st = stages + (size_t)slot * C::STAGE_ELEMS;
@@ -372,7 +375,15 @@ gemmPassKernel(const GemmArgs<T> a, const __grid_constant__ CUtensorMap tmap) {
       const bool useY = epi && a.beta != T(0) && a.Y != nullptr;
       // Common case first and kept short (the steady-state loop has to stay small enough
       // for the instruction cache): plain pass, no epilogue, no redistribution.
-      if (!epi && a.sc.parts == 0 && (XT || a.mode == 0)) {
+      if ((ABL & 1) && a.numTiles != 0xFFFFFFFFull) {
+        // ablation: keep the accumulators alive without storing them
+        T sum = T(0);
+#pragma unroll
+        for (int qi = 0; qi < MQ; qi++)
+#pragma unroll
+          for (int ji = 0; ji < MJ; ji++) sum += XT ? acc.at(qi, ji) : acc.at(qi, ji);
+        if (sum == T(12345.678)) a.Z[0] = sum;
+      } else if (!epi && a.sc.parts == 0 && (XT || a.mode == 0)) {
         if constexpr (!XT) {
           const unsigned nn = t / tpc, bt = t - nn * tpc;
           T* p0 = a.Z + nn * QB + (unsigned long long)bt * TJ + tj * VEC + (unsigned long long)(tq * VEC) * a.B;

@@ -2,6 +2,7 @@
 // kernel_tile_{f32,f64}_{narrow,wide}.cu).
 #include "kernels.h"
 #include "tile_table.h"
+#include "tile_db.h"
 
 namespace fkb {
 
@@ -18,6 +19,8 @@ extern template fastKronError launchTileTr<float, 1>(const Pass&, const LaunchCt
 extern template fastKronError launchTileTr<float, 2>(const Pass&, const LaunchCtx&);
 extern template fastKronError launchTileTr<double, 1>(const Pass&, const LaunchCtx&);
 extern template fastKronError launchTileTr<double, 2>(const Pass&, const LaunchCtx&);
+
+int tileTmaTimeouts();     // kernel_tile_f32_wide.cu, the only unit with TMA-staged tile kernels
 
 bool tileSupported(DType dt, uint32_t P, int nf, int tileB) {
   (void)dt;
@@ -50,3 +53,14 @@ fastKronError launchTile(const Pass& ps, const LaunchCtx& cx) {
 }
 
 }  // namespace fkb
+
+// Tuner hook (fastkron_b200/tune.py): force one (tile KB, ring depth, CTAs per SM, TMA) choice on
+// every tile kernel launched by this process; kb = 0 returns to the swept table.
+extern "C" void fkbSetTileTuning(int kb, int nbuf, int minb, int tma) {
+  fkb::TileTune& o = fkb::tileTuneOverride();
+  o.kb = kb; o.nbuf = nbuf == 1 ? 1 : 2; o.minb = minb; o.tma = tma;
+}
+
+// Non-zero if a bounded wait on a tile barrier of the TMA-staged tile kernels ever gave up
+// in this process on the current device (tests).
+extern "C" int fkbTileTmaTimeouts() { return fkb::tileTmaTimeouts(); }

@@ -45,24 +45,16 @@ struct TileArgs {
   int epilogue;
 };
 
-#ifndef FKB_TILE_THREADS
-#define FKB_TILE_THREADS 128
-#endif
-#ifndef FKB_TILE_MINB
-#define FKB_TILE_MINB 4
-#endif
-constexpr int kTileThreads = FKB_TILE_THREADS;
-constexpr int kTileMinBlocks = FKB_TILE_MINB;
-#ifndef FKB_STEP_UNROLL
-#define FKB_STEP_UNROLL 4
-#endif
-constexpr int kStepUnroll = FKB_STEP_UNROLL;   // p iterations unrolled in a contraction step
+constexpr int kTileThreads = 128;
+constexpr int kTileMinBlocks = 3;     // two tile buffers of ~32 KB per CTA: three CTAs per SM
+constexpr int kStepUnroll = 4;        // p iterations unrolled in a contraction step
 constexpr int kTileMaxR = 64;
 
 __host__ __device__ constexpr int ipow(int b, int e) { return e == 0 ? 1 : b * ipow(b, e - 1); }
 
-template <typename T>
+template <typename T, bool SWZ = true>
 __host__ __device__ constexpr unsigned physIdx(unsigned idx) {
+  if (!SWZ) return idx;                          // linear tile (filled by TMA; wide layouts only)
   constexpr int LB = (sizeof(T) == 4) ? 5 : 4;   // log2(elements per 128-byte line)
   constexpr int VB = (sizeof(T) == 4) ? 2 : 1;   // log2(elements per 16-byte chunk)
   const unsigned line = idx >> LB;
@@ -86,10 +78,7 @@ struct alignas(W * sizeof(T)) VecW {
 // outputs (64 floats / 32 doubles), i.e. kAcc/P whole fibres.
 template <typename T>
 struct StepShape {
-#ifndef FKB_TILE_ACC_BYTES
-#define FKB_TILE_ACC_BYTES 256
-#endif
-  static constexpr int kAcc = FKB_TILE_ACC_BYTES / (int)sizeof(T);
+  static constexpr int kAcc = 256 / (int)sizeof(T);
 };
 template <typename T, int P>
 __host__ __device__ constexpr int stepFibres() { return StepShape<T>::kAcc / P > 0 ? StepShape<T>::kAcc / P : 1; }
@@ -120,7 +109,7 @@ __host__ __device__ __forceinline__ void schedFence() {
 // fp32 steps use the packed FMA of sm_100 (fma.rn.f32x2: two independent IEEE fp32 FMAs per
 // lane and instruction, bit-identical to two scalar FMAs) on the device; the host build of
 // these templates (the CPU emulation of the tile kernels) keeps the scalar form.
-#if defined(__CUDA_ARCH__) && !defined(FKB_NO_FFMA2)
+#if defined(__CUDA_ARCH__)
 constexpr bool kPackedFma = true;
 #else
 constexpr bool kPackedFma = false;
@@ -201,7 +190,7 @@ struct FibreAcc<float, U, W, P, FV, 2> {
 // Strided fibres, S >= W: a thread owns NFIB = kAcc/P fibres, as U groups of W
 // neighbouring ones (W * sizeof(T) <= 16 bytes); every access is one W-wide
 // shared-memory transaction, consecutive lanes take consecutive groups.
-template <typename T, int P, int S, int THREADS>
+template <typename T, int P, int S, int THREADS, bool SWZ = true>
 __host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const T* __restrict__ Fs, int E, int tid) {
   constexpr int VEC = Vec16<T>::N;
   constexpr int NFIB = stepFibres<T, P>();
@@ -221,7 +210,7 @@ __host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const
       if (!ok[u]) vg = vg0;
       const unsigned lo = (unsigned)vg % (S / W);
       const unsigned hi = (unsigned)vg / (S / W);
-      pb[u] = physIdx<T>(hi * (unsigned)(S * P) + lo * W);
+      pb[u] = physIdx<T, SWZ>(hi * (unsigned)(S * P) + lo * W);
     }
     constexpr int ACC_MODE = !(kPackedFma && sizeof(T) == 4) ? 0
                              : (FV % 2 == 0 && U * W < P)    ? 2
@@ -236,7 +225,7 @@ __host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const
       V xv[U];
 #pragma unroll
       for (int u = 0; u < U; u++)
-        xv[u] = *reinterpret_cast<const V*>(tile + (pb[u] ^ physIdx<T>((unsigned)(p * S))));
+        xv[u] = *reinterpret_cast<const V*>(tile + (pb[u] ^ physIdx<T, SWZ>((unsigned)(p * S))));
 #pragma unroll
       for (int q0 = 0; q0 < P; q0 += FV) {
         T f[FV];
@@ -260,7 +249,7 @@ __host__ __device__ __forceinline__ void stepStrided(T* __restrict__ tile, const
         V ov;
 #pragma unroll
         for (int k = 0; k < W; k++) ov.v[k] = acc.at(u, k, q);
-        if (ok[u]) *reinterpret_cast<V*>(tile + (pb[u] ^ physIdx<T>((unsigned)(q * S)))) = ov;
+        if (ok[u]) *reinterpret_cast<V*>(tile + (pb[u] ^ physIdx<T, SWZ>((unsigned)(q * S)))) = ov;
       }
     }
   }
@@ -305,7 +294,7 @@ struct RowAcc<float, NFIB, P, true> {
 
 // Contiguous fibres (S == 1, P >= VEC): a thread owns NFIB whole fibres, reads
 // and writes them as 128-bit pieces along p / q.
-template <typename T, int P, int THREADS>
+template <typename T, int P, int THREADS, bool SWZ = true>
 __host__ __device__ __forceinline__ void stepContig(T* __restrict__ tile, const T* __restrict__ Fs, int E, int tid) {
   constexpr int VEC = Vec16<T>::N;
   constexpr int NFIB = stepFibres<T, P>();
@@ -319,7 +308,7 @@ __host__ __device__ __forceinline__ void stepContig(T* __restrict__ tile, const 
       int f = f0 + k * THREADS;
       ok[k] = f < nfib;
       if (!ok[k]) f = f0;
-      pb[k] = physIdx<T>((unsigned)f * P);
+      pb[k] = physIdx<T, SWZ>((unsigned)f * P);
     }
     RowAcc<T, NFIB, P, kPackedFma> acc;
     acc.clear();
@@ -329,7 +318,7 @@ __host__ __device__ __forceinline__ void stepContig(T* __restrict__ tile, const 
       V xv[NFIB];
 #pragma unroll
       for (int k = 0; k < NFIB; k++)
-        xv[k] = *reinterpret_cast<const V*>(tile + (pb[k] ^ physIdx<T>((unsigned)p0)));
+        xv[k] = *reinterpret_cast<const V*>(tile + (pb[k] ^ physIdx<T, SWZ>((unsigned)p0)));
 #pragma unroll
       for (int pp = 0; pp < VEC; pp++) {
 #pragma unroll
@@ -348,7 +337,7 @@ __host__ __device__ __forceinline__ void stepContig(T* __restrict__ tile, const 
         V ov;
 #pragma unroll
         for (int i = 0; i < VEC; i++) ov.v[i] = acc.at(k, q0 + i);
-        if (ok[k]) *reinterpret_cast<V*>(tile + (pb[k] ^ physIdx<T>((unsigned)q0))) = ov;
+        if (ok[k]) *reinterpret_cast<V*>(tile + (pb[k] ^ physIdx<T, SWZ>((unsigned)q0))) = ov;
       }
     }
   }
@@ -357,7 +346,7 @@ __host__ __device__ __forceinline__ void stepContig(T* __restrict__ tile, const 
 // Any stride, any P: one fibre per thread with scalar accesses.  Only reached
 // for the few shapes the vector steps cannot express (P or S below one 16-byte
 // chunk).
-template <typename T, int P, int S, int THREADS>
+template <typename T, int P, int S, int THREADS, bool SWZ = true>
 __host__ __device__ __forceinline__ void stepScalar(T* __restrict__ tile, const T* __restrict__ Fs, int E, int tid) {
   const int nfib = E / P;
   for (int f = tid; f < nfib; f += THREADS) {
@@ -366,7 +355,7 @@ __host__ __device__ __forceinline__ void stepScalar(T* __restrict__ tile, const 
     const unsigned base = hi * (unsigned)(S * P) + lo;
     T x[P], o[P];
 #pragma unroll
-    for (int p = 0; p < P; p++) x[p] = tile[physIdx<T>(base + (unsigned)(p * S))];
+    for (int p = 0; p < P; p++) x[p] = tile[physIdx<T, SWZ>(base + (unsigned)(p * S))];
 #pragma unroll
     for (int q = 0; q < P; q++) {
       T acc = T(0);
@@ -375,7 +364,7 @@ __host__ __device__ __forceinline__ void stepScalar(T* __restrict__ tile, const 
       o[q] = acc;
     }
 #pragma unroll
-    for (int q = 0; q < P; q++) tile[physIdx<T>(base + (unsigned)(q * S))] = o[q];
+    for (int q = 0; q < P; q++) tile[physIdx<T, SWZ>(base + (unsigned)(q * S))] = o[q];
   }
 }
 
@@ -498,10 +487,10 @@ __device__ __forceinline__ void stepDmma8Pair(double* __restrict__ tile, const d
 }
 #endif
 
-template <typename T, int P, int S, int THREADS>
+template <typename T, int P, int S, int THREADS, bool SWZ = true>
 __host__ __device__ __forceinline__ void stepDispatch(T* tile, const T* Fs, int E, int tid) {
-#if defined(__CUDA_ARCH__) && !defined(FKB_NO_DMMA)
-  if constexpr (sizeof(T) == 8 && P == 8 && (S == 1 || S % 8 == 0)) {
+#if defined(__CUDA_ARCH__)
+  if constexpr (SWZ && sizeof(T) == 8 && P == 8 && (S == 1 || S % 8 == 0)) {
     stepDmma8<S, THREADS>(tile, Fs, E, tid);
     return;
   }
@@ -510,39 +499,39 @@ __host__ __device__ __forceinline__ void stepDispatch(T* tile, const T* Fs, int 
   constexpr int NFIB = stepFibres<T, P>();
   constexpr int W = NFIB < VEC ? NFIB : VEC;
   if constexpr (S >= W && S % W == 0) {
-    stepStrided<T, P, S, THREADS>(tile, Fs, E, tid);
+    stepStrided<T, P, S, THREADS, SWZ>(tile, Fs, E, tid);
   } else if constexpr (S == 1 && P >= VEC) {
-    stepContig<T, P, THREADS>(tile, Fs, E, tid);
+    stepContig<T, P, THREADS, SWZ>(tile, Fs, E, tid);
   } else {
-    stepScalar<T, P, S, THREADS>(tile, Fs, E, tid);
+    stepScalar<T, P, S, THREADS, SWZ>(tile, Fs, E, tid);
   }
 }
 
 // Apply factors J, J-1, ..., 0 of the group (J = NF-1 first).
-template <typename T, int P, int NF, int BT, int THREADS, int J>
+template <typename T, int P, int NF, int BT, int THREADS, int J, bool SWZ = true>
 struct StepChain {
   static __device__ __forceinline__ void run(T* tile, const T* Fs, int E) {
     constexpr int S = ipow(P, NF - 1 - J) * BT;
-#if defined(__CUDA_ARCH__) && !defined(FKB_NO_DMMA)
-    if constexpr (sizeof(T) == 8 && P == 8 && J >= 1 && (S == 1 || S % 8 == 0)) {
+#if defined(__CUDA_ARCH__)
+    if constexpr (SWZ && sizeof(T) == 8 && P == 8 && J >= 1 && (S == 1 || S % 8 == 0)) {
       // factors J and J-1 together, intermediate in registers
       stepDmma8Pair<S, THREADS>(tile, Fs + J * P * P, Fs + (J - 1) * P * P, E, (int)threadIdx.x);
       __syncthreads();
-      StepChain<T, P, NF, BT, THREADS, J - 2>::run(tile, Fs, E);
+      StepChain<T, P, NF, BT, THREADS, J - 2, SWZ>::run(tile, Fs, E);
       return;
     }
 #endif
-    stepDispatch<T, P, S, THREADS>(tile, Fs + J * P * P, E, (int)threadIdx.x);
+    stepDispatch<T, P, S, THREADS, SWZ>(tile, Fs + J * P * P, E, (int)threadIdx.x);
     __syncthreads();
-    StepChain<T, P, NF, BT, THREADS, J - 1>::run(tile, Fs, E);
+    StepChain<T, P, NF, BT, THREADS, J - 1, SWZ>::run(tile, Fs, E);
   }
 };
-template <typename T, int P, int NF, int BT, int THREADS>
-struct StepChain<T, P, NF, BT, THREADS, -1> {
+template <typename T, int P, int NF, int BT, int THREADS, bool SWZ>
+struct StepChain<T, P, NF, BT, THREADS, -1, SWZ> {
   static __device__ __forceinline__ void run(T*, const T*, int) {}
 };
-template <typename T, int P, int NF, int BT, int THREADS>
-struct StepChain<T, P, NF, BT, THREADS, -2> {
+template <typename T, int P, int NF, int BT, int THREADS, bool SWZ>
+struct StepChain<T, P, NF, BT, THREADS, -2, SWZ> {
   static __device__ __forceinline__ void run(T*, const T*, int) {}
 };
 
@@ -625,20 +614,78 @@ __device__ __forceinline__ void tileVectorAt(const unsigned long long* bases, un
   }
 }
 
-template <typename T, int P, int NF, bool WIDE>
-__global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tilePassKernel(const TileArgs<T> a) {
+// mbarrier / TMA primitives for the tile ring (one CTA, no multicast).
+// Set when a bounded wait on a tile barrier gave up.  One copy per translation unit; only the
+// unit that instantiates TMA-staged kernels (fp32 wide) ever writes it.
+static __device__ int gTileTmaTimeouts = 0;
+__device__ __forceinline__ void tileMbarInit(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"((unsigned)__cvta_generic_to_shared(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void tileMbarExpectTx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"((unsigned)__cvta_generic_to_shared(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool tileMbarTryWait(unsigned long long* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"((unsigned)__cvta_generic_to_shared(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Gives up after about two seconds, records that and reports failure.
+__device__ __forceinline__ bool tileMbarWaitBounded(unsigned long long* bar, unsigned parity) {
+  if (tileMbarTryWait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!tileMbarTryWait(bar, parity)) {
+    if (clock64() - t0 > 4000000000ll) { atomicExch(&gTileTmaTimeouts, 1); return false; }
+  }
+  return true;
+}
+// One box {BT, rows, 1} of the [chunks][G][B] view at (x = b0, y = g0, z = chunk).
+__device__ __forceinline__ void tileTmaLoad(void* smemDst, const void* tmap, int x, int y, int z, unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+      ::"r"((unsigned)__cvta_generic_to_shared(smemDst)), "l"(tmap), "r"(x), "r"(y), "r"(z),
+        "r"((unsigned)__cvta_generic_to_shared(bar)) : "memory");
+}
+
+struct alignas(64) TileTmaMap { unsigned char bytes[128]; };   // a CUtensorMap, kept opaque here
+
+// The pass kernel.  Persistent CTAs walk super-tiles with a ring of two tile buffers: while the
+// contraction steps and the stores of super-tile t run, super-tile t+1 is already on its way
+// into the other buffer, so a CTA never sits idle waiting for memory once the ring is primed.
+// Staging:
+//   TMA == false  16-byte cp.async from every thread into the XOR-swizzled layout (any layout;
+//                 the narrow steps and the DMMA steps need the swizzle)
+//   TMA == true   wide fp32 tiles: lanes of a warp always run along the trailing index there, so
+//                 a linear [G][W] sub-tile is already free of bank conflicts and one elected
+//                 thread can stage it with cp.async.bulk.tensor (boxes of up to 256 rows of 128
+//                 bytes, completion on an mbarrier with a bounded wait)
+template <typename T, int P, int NF, bool WIDE, bool TMA, int MINB = kTileMinBlocks, int NBUF = 2>
+__global__ void __launch_bounds__(kTileThreads, MINB)
+tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap) {
   constexpr int THREADS = kTileThreads;
   constexpr int VEC = Vec16<T>::N;
   constexpr int BT = WIDE ? (int)(128 / sizeof(T)) : 1;
   constexpr int G = ipow(P, NF);
   constexpr int SUB = G * BT;
+  constexpr bool SWZ = !TMA;
+  constexpr int BOXR = G < 256 ? G : 256;             // rows of one TMA box
+  static_assert(!TMA || (WIDE && sizeof(T) == 4), "TMA staging: wide fp32 tiles");
   using V = Vec16<T>;
 
   extern __shared__ __align__(1024) unsigned char smemRaw[];
-  T* tile = reinterpret_cast<T*>(smemRaw);
-  T* Fs = tile + (size_t)a.R * SUB;
-  unsigned long long* bases = reinterpret_cast<unsigned long long*>(Fs + NF * P * P);
+  const size_t tileElems = (size_t)a.R * SUB;
+  static_assert(NBUF == 1 || NBUF == 2, "one tile buffer (load, compute, store in turn) or a ring of two");
+  T* tiles = reinterpret_cast<T*>(smemRaw);           // NBUF buffers of tileElems
+  T* Fs = tiles + NBUF * tileElems;
+  unsigned long long* basesAll = reinterpret_cast<unsigned long long*>(Fs + NF * P * P);   // [2][kTileMaxR]
+  __shared__ __align__(8) unsigned long long fullBar[2];
 
+  if (TMA && threadIdx.x == 0) {
+    tileMbarInit(&fullBar[0], 1);
+    tileMbarInit(&fullBar[1], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
   // factors -> shared memory as [k][p][q]
   for (int i = threadIdx.x; i < NF * P * P; i += THREADS) {
     const int k = i / (P * P), p = (i / P) % P, q = i % P;
@@ -646,26 +693,99 @@ __global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tilePassKernel(c
   }
 
   const unsigned long long R = (unsigned long long)a.R;
-  for (unsigned long long st0 = (unsigned long long)blockIdx.x * R; st0 < a.numSub;
-       st0 += (unsigned long long)gridDim.x * R) {
+  const unsigned long long stride = (unsigned long long)gridDim.x * R;
+
+  // Bases of the sub-tiles of the super-tile that starts at st0, and its loads into buffer b.
+  auto stage = [&](unsigned long long st0, int b) {
     const unsigned long long left = a.numSub - st0;
     const int nsub = left < R ? (int)left : (int)R;
-    if (WIDE && (int)threadIdx.x < nsub) {
-      const unsigned long long st = st0 + threadIdx.x;
-      const unsigned long long chunk = st / a.tilesPerChunk;
-      const unsigned long long bt = st % a.tilesPerChunk;
-      bases[threadIdx.x] = chunk * (unsigned long long)G * a.B + bt * (unsigned long long)BT;
+    unsigned long long* bases = basesAll + b * kTileMaxR;
+    T* tile = tiles + (size_t)b * tileElems;
+    if constexpr (TMA) {
+      if (threadIdx.x == 0) {
+        tileMbarExpectTx(&fullBar[b], (unsigned)(nsub * SUB * sizeof(T)));
+        for (int r = 0; r < nsub; r++) {
+          const unsigned long long st = st0 + r;
+          const unsigned long long chunk = st / a.tilesPerChunk, bt = st % a.tilesPerChunk;
+          bases[r] = chunk * (unsigned long long)G * a.B + bt * (unsigned long long)BT;
+#pragma unroll
+          for (int g0 = 0; g0 < G; g0 += BOXR)
+            tileTmaLoad(tile + (size_t)r * SUB + (size_t)g0 * BT, &tmap, (int)(bt * BT), g0, (int)chunk, &fullBar[b]);
+        }
+      }
+    } else {
+      if constexpr (WIDE) {
+        // every thread derives the base of the sub-tiles it copies itself (sharing them through
+        // shared memory would need a barrier in the middle of the other buffer's arithmetic)
+        constexpr int VPS = SUB / VEC;
+        auto subBase = [&](unsigned long long st) -> unsigned long long {
+          if (a.numSub <= 0xFFFFFFFFull) {
+            const unsigned s32 = (unsigned)st, t32 = (unsigned)a.tilesPerChunk;
+            const unsigned c = s32 / t32, bt = s32 - c * t32;
+            return (unsigned long long)c * (unsigned long long)G * a.B + (unsigned long long)bt * BT;
+          }
+          return (st / a.tilesPerChunk) * (unsigned long long)G * a.B + (st % a.tilesPerChunk) * (unsigned long long)BT;
+        };
+        if constexpr (VPS >= THREADS) {
+          for (int r = 0; r < nsub; r++) {
+            const unsigned long long base = subBase(st0 + r);
+            if (threadIdx.x == 0) bases[r] = base;
+#pragma unroll 4
+            for (int j = threadIdx.x; j < VPS; j += THREADS) {
+              const unsigned w = (unsigned)j * VEC;
+              cpAsync16(tile + physIdx<T, SWZ>((unsigned)r * SUB + w), a.X + base + (unsigned long long)(w / BT) * a.B + (w % BT));
+            }
+          }
+        } else {
+          constexpr int SPT = THREADS / VPS;
+          const unsigned w = (threadIdx.x % VPS) * VEC;
+          const unsigned long long gw = (unsigned long long)(w / BT) * a.B + (w % BT);
+          for (int r = threadIdx.x / VPS; r < nsub; r += SPT) {
+            const unsigned long long base = subBase(st0 + r);
+            if (w == 0) bases[r] = base;
+            cpAsync16(tile + physIdx<T, SWZ>((unsigned)r * SUB + w), a.X + base + gw);
+          }
+        }
+      } else {
+        forEachTileVector<T, WIDE, SUB, BT, THREADS>(bases, st0 * G, nsub, a.B, [&](unsigned idx, unsigned long long goff) {
+          cpAsync16(tile + physIdx<T, SWZ>(idx), a.X + goff);
+        });
+      }
+    }
+  };
+
+  unsigned long long st0 = (unsigned long long)blockIdx.x * R;
+  if (NBUF == 2) {
+    if (st0 < a.numSub) stage(st0, 0);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  }
+  unsigned phases = 0;
+  for (int it = 0; st0 < a.numSub; st0 += stride, it++) {
+    const int b = NBUF == 2 ? (it & 1) : 0;
+    const unsigned long long left = a.numSub - st0;
+    const int nsub = left < R ? (int)left : (int)R;
+    if (NBUF == 2) {
+      // the other buffer's previous contents were stored before the barrier that ended the last
+      // iteration: refill it now, then wait for this iteration's tile only
+      if (st0 + stride < a.numSub) stage(st0 + stride, b ^ 1);
+    } else {
+      stage(st0, 0);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    if constexpr (TMA) {
+      if (!tileMbarWaitBounded(&fullBar[b], (phases >> b) & 1u)) return;
+      phases ^= 1u << b;
+    } else if (NBUF == 2) {
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     }
     __syncthreads();
 
+    T* tile = tiles + (size_t)b * tileElems;
+    const unsigned long long* bases = basesAll + b * kTileMaxR;
     const int E = nsub * SUB;
-    forEachTileVector<T, WIDE, SUB, BT, THREADS>(bases, st0 * G, nsub, a.B, [&](unsigned idx, unsigned long long goff) {
-      cpAsync16(tile + physIdx<T>(idx), a.X + goff);
-    });
-    cpAsyncWaitAll();
-    __syncthreads();
-
-    StepChain<T, P, NF, BT, THREADS, NF - 1>::run(tile, Fs, E);
+    StepChain<T, P, NF, BT, THREADS, NF - 1, SWZ>::run(tile, Fs, E);
 
     const bool epi = a.epilogue != 0;
     const bool useY = epi && a.beta != T(0) && a.Y != nullptr;
@@ -690,7 +810,7 @@ __global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tilePassKernel(c
           if (i0 + e < cnt) {
             unsigned idx; unsigned long long go;         // recomputed: cheaper than keeping EB offsets live
             tileVectorAt<T, WIDE, SUB, BT, THREADS>(bases, st0 * G, a.B, i0 + e, idx, go);
-            V o = *reinterpret_cast<const V*>(tile + physIdx<T>(idx));
+            V o = *reinterpret_cast<const V*>(tile + physIdx<T, SWZ>(idx));
 #pragma unroll
             for (int i = 0; i < VEC; i++) o.v[i] = fma(a.beta, y[e].v[i], a.alpha * o.v[i]);
             *reinterpret_cast<V*>(a.Z + go) = o;
@@ -699,20 +819,16 @@ __global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tilePassKernel(c
       }
     } else
     forEachTileVector<T, WIDE, SUB, BT, THREADS>(bases, st0 * G, nsub, a.B, [&](unsigned idx, unsigned long long goff) {
-      V o = *reinterpret_cast<const V*>(tile + physIdx<T>(idx));
+      V o = *reinterpret_cast<const V*>(tile + physIdx<T, SWZ>(idx));
       if (epi) {
 #pragma unroll
         for (int i = 0; i < VEC; i++) o.v[i] = a.alpha * o.v[i];
-        if (useY) {
-          const V y = *reinterpret_cast<const V*>(a.Y + goff);
-#pragma unroll
-          for (int i = 0; i < VEC; i++) o.v[i] = fma(a.beta, y.v[i], o.v[i]);
-        }
       }
       *reinterpret_cast<V*>(a.Z + goff) = o;
     });
     __syncthreads();
   }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 }
 
 // ---- transposing variant ---------------------------------------------------------

@@ -2,10 +2,78 @@
 // that each (type, layout) pair compiles in its own translation unit.
 #pragma once
 
+#include <cuda.h>            // CUtensorMap (type only; the encoder is fetched at run time)
+#include <string.h>
+#include <stdlib.h>
+
 #include "kernel_tile.cuh"
 #include "tile_table.h"
+#include "tile_db.h"
 
 namespace fkb {
+
+// cuTensorMapEncodeTiled from the driver, without linking libcuda.
+typedef CUresult (*TileEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline TileEncodeFn tileMapEncoder() {
+  static TileEncodeFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<TileEncodeFn>(p);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// Tensor map over a wide pass's input viewed as [chunks][G][B] fp32, box {32, min(G, 256), 1}.
+inline bool encodeTileMap(TileTmaMap* out, const void* X, unsigned long long chunks, unsigned G, unsigned long long B) {
+  static_assert(sizeof(CUtensorMap) <= sizeof(TileTmaMap), "tensor map size");
+  TileEncodeFn enc = tileMapEncoder();
+  if (!enc || B > 0xFFFFFFFFull || chunks > 0x7FFFFFFFull || (B * 4) % 16 != 0) return false;
+  const cuuint64_t dims[3] = {B, G, chunks};
+  const cuuint64_t strides[2] = {B * 4, (cuuint64_t)G * B * 4};
+  const cuuint32_t box[3] = {32, G < 256 ? G : 256, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return enc(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(X), dims, strides, box,
+             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, int P, int NF, bool WIDE, bool TMA, int MINB = kTileMinBlocks, int NBUF = 2>
+static fastKronError launchTileKernel(const TileArgs<T>& a, const TileTmaMap& tm, size_t smem, unsigned long long supers,
+                                      const LaunchCtx& cx) {
+  auto kern = tilePassKernel<T, P, NF, WIDE, TMA, MINB, NBUF>;
+  // per device: the shared-memory opt-in, and the occupancy for the last tile size seen
+  static bool attrSetDev[kMaxDevices] = {false};
+  static size_t occSmemDev[kMaxDevices] = {0};
+  static int occDev[kMaxDevices] = {0};
+  const int dev = currentDeviceSlot();
+  if (!attrSetDev[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return cudaToFk(e);
+    attrSetDev[dev] = true;
+  }
+  if (occSmemDev[dev] != smem || occDev[dev] < 1) {
+    int q = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, kern, kTileThreads, smem) != cudaSuccess || q < 1) {
+      cudaGetLastError();
+      return fastKronKernelNotFound;
+    }
+    occSmemDev[dev] = smem; occDev[dev] = q;
+  }
+  const int n = occDev[dev];
+  unsigned long long grid = (unsigned long long)cx.smCount * n;
+  if (grid > supers) grid = supers;
+  kern<<<(unsigned)grid, kTileThreads, smem, cx.stream>>>(a, tm);
+  return cudaToFk(cudaGetLastError());
+}
 
 template <typename T, int P, int NF, bool WIDE>
 static fastKronError launchTileOne(const Pass& ps, const LaunchCtx& cx) {
@@ -25,30 +93,34 @@ static fastKronError launchTileOne(const Pass& ps, const LaunchCtx& cx) {
   a.alpha = (T)cx.alpha; a.beta = (T)cx.beta; a.epilogue = ps.epilogue ? 1 : 0;
   if (a.numSub == 0) return fastKronSuccess;
 
-  // super-tile of about 32 KB (64 KB for P = 32, whose thread items are larger),
-  // shrunk while the grid would leave SMs idle
-  const size_t target = (P == 32 ? 64 : 32) * 1024;
-  long long R = ps.tileR > 1 ? ps.tileR : (long long)(target / (SUB * es));
+  // tile size, ring depth and CTAs per SM of this kernel: the swept table, or the tuner's override
+  const TileTune tn = tileTuneFor(sizeof(T) == 4 ? DType::F32 : DType::F64, P, NF, WIDE);
+  const size_t target = (size_t)tn.kb * 1024;
+  long long R = (long long)(target / (SUB * es));
   if (R < 1) R = 1;
   if (WIDE && R > kTileMaxR) R = kTileMaxR;      // wide sub-tiles keep a table of bases
-  while (R > 1 && (a.numSub + R - 1) / R < (unsigned long long)cx.smCount * 4) R >>= 1;
+  // shrunk while the grid would leave SMs idle
+  while (R > 1 && (a.numSub + R - 1) / R < (unsigned long long)cx.smCount * 3) R >>= 1;
   a.R = (int)R;
 
-  const size_t smem = (size_t)R * SUB * es + (size_t)NF * P * P * es + kTileMaxR * sizeof(unsigned long long);
-  auto kern = tilePassKernel<T, P, NF, WIDE>;
-  static bool attrSetDev[kMaxDevices] = {false};
-  bool& attrSet = attrSetDev[currentDeviceSlot()];
-  if (!attrSet) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) return cudaToFk(e);
-    attrSet = true;
-  }
+  const size_t smem = (size_t)tn.nbuf * R * SUB * es + (size_t)NF * P * P * es + 2 * kTileMaxR * sizeof(unsigned long long);
   if (smem > 200 * 1024) return fastKronKernelNotFound;
-  unsigned long long supers = (a.numSub + R - 1) / R;
-  const unsigned long long cap = (unsigned long long)cx.smCount * 16;
-  if (supers > cap) supers = cap;
-  kern<<<(unsigned)supers, kTileThreads, smem, cx.stream>>>(a);
-  return cudaToFk(cudaGetLastError());
+  const unsigned long long supers = (a.numSub + R - 1) / R;
+  TileTmaMap tm;
+  memset(&tm, 0, sizeof(tm));
+  if constexpr (WIDE && sizeof(T) == 4) {
+    // TMA staging needs the ring (its point is to overlap the next tile's transfer)
+    if (tn.nbuf == 2 && tn.tma && encodeTileMap(&tm, a.X, chunks, (unsigned)G, a.B)) {
+      if (tn.minb >= 4) return launchTileKernel<T, P, NF, WIDE, true, 4, 2>(a, tm, smem, supers, cx);
+      return launchTileKernel<T, P, NF, WIDE, true, 3, 2>(a, tm, smem, supers, cx);
+    }
+  }
+  if (tn.nbuf == 1) {
+    if (tn.minb >= 6) return launchTileKernel<T, P, NF, WIDE, false, 6, 1>(a, tm, smem, supers, cx);
+    return launchTileKernel<T, P, NF, WIDE, false, 4, 1>(a, tm, smem, supers, cx);
+  }
+  if (tn.minb >= 4) return launchTileKernel<T, P, NF, WIDE, false, 4, 2>(a, tm, smem, supers, cx);
+  return launchTileKernel<T, P, NF, WIDE, false, 3, 2>(a, tm, smem, supers, cx);
 }
 
 template <typename T, bool WIDE>

@@ -19,6 +19,7 @@
 #include "fk_common.h"
 #include "tile_table.h"
 #include "gemm_table.h"
+#include "tile_db.h"
 
 #include <sstream>
 #include <stdlib.h>
@@ -42,42 +43,48 @@ static Layout matLayout(const Problem& pr, uint64_t cols) {
 
 struct TileChoice { int nf; int tileB; int tileR; };
 
-// How many equal factors to fuse for the shared-memory tile kernel.  `avail`
-// equal factors are available; B is the (folded) trailing extent.  The choice is
-// limited to the kernels that exist (tile_table.h): narrow tiles fuse while one
-// [P^nf] block stays within 32 KB, wide tiles while [P^nf][128 bytes] stays
-// within 64 KB.  Returns nf == 0 when no kernel fits.
-static TileChoice chooseTile(DType dt, uint32_t P, int avail, uint64_t B, bool fusion) {
+// Tuner hook (fastkron_b200/tune.py): cap on the fusion depth of every plan made by this
+// process; 0 = none.
+static int gMaxFuseOverride = 0;
+void setMaxFuseOverride(int cap) { gMaxFuseOverride = cap > 0 ? cap : 0; }
+
+// How many equal factors to fuse for the shared-memory tile kernel.  `avail` equal factors are
+// available; B is the (folded) trailing extent.  The choice is limited to the kernels that
+// exist (tile_table.h) and whose tile fits: narrow tiles fuse while one [P^nf] block stays
+// within 32 KB, wide tiles while [P^nf][128 bytes] stays within 64 KB.  Among the depths that
+// fit, the swept table (tile_db.h: fusion depth per element type, P, layout and number of
+// factors left) decides; shapes the sweep did not visit spread the factors evenly over the
+// passes they need anyway (a pass's time grows with its depth, its memory traffic does not).
+// Returns nf == 0 when no kernel fits.
+static TileChoice chooseTile(DType dt, uint32_t P, int avail, uint64_t B, bool fusion, int maxFuse) {
   const size_t es = dtypeSize(dt);
   TileChoice c{0, 1, 0};
   const bool wide = B > 1;
   if (!fusion) avail = 1;
   if (avail > kMaxGroup) avail = kMaxGroup;
-  // FASTKRON_MAX_FUSE caps the fusion depth (tuning / experiments)
-  if (const char* cap = getenv("FASTKRON_MAX_FUSE")) { const int c2 = atoi(cap); if (c2 >= 1 && c2 < avail) avail = c2; }
+  const int left = avail;                       // factors of the run still to be applied
+  if (maxFuse > 0 && maxFuse < avail) avail = maxFuse;
+  if (gMaxFuseOverride > 0 && gMaxFuseOverride < avail) avail = gMaxFuseOverride;
   if (wide) {
     const uint64_t W = 128 / es;
     if (B % W != 0) return c;
     c.tileB = (int)W;
-    for (int nf = avail; nf >= 1; nf--) {
-      if (!tileInTable(P, nf, true)) continue;
-      uint64_t g = 1; for (int k = 0; k < nf; k++) g *= P;
-      if (g * 128 <= 64 * 1024) { c.nf = nf; break; }
-    }
-  } else {
-    for (int nf = avail; nf >= 1; nf--) {
-      if (!tileInTable(P, nf, false)) continue;
-      uint64_t g = 1; for (int k = 0; k < nf; k++) g *= P;
-      if (g * es <= 32 * 1024 && (g * es) % 16 == 0) { c.nf = nf; break; }
-    }
   }
-  // Balance: when the run of equal factors needs several passes anyway, spread the factors
-  // evenly over them (measured on B200: 16x16^4 as 2+2 beats 3+1, 8x8^8 as 4+2+2 ties 4+3+1),
-  // because a pass's time grows with its depth while its memory traffic does not.
-  if (c.nf >= 1 && c.nf < avail) {
-    const int passes = (avail + c.nf - 1) / c.nf;
-    int even = (avail + passes - 1) / passes;
-    while (even >= 1 && !tileInTable(P, even, wide)) even--;
+  auto fits = [&](int nf) {
+    if (!tileInTable(P, nf, wide)) return false;
+    uint64_t g = 1; for (int k = 0; k < nf; k++) g *= P;
+    return wide ? g * 128 <= 64 * 1024 : (g * es <= 32 * 1024 && (g * es) % 16 == 0);
+  };
+  int deepest = 0;
+  for (int nf = avail; nf >= 1; nf--) if (fits(nf)) { deepest = nf; break; }
+  if (deepest == 0) return c;
+  c.nf = deepest;
+  const int swept = tileFuseDepth(dt, P, wide, left);
+  if (swept >= 1 && swept <= deepest && fits(swept)) { c.nf = swept; return c; }
+  if (c.nf < left) {
+    const int passes = (left + c.nf - 1) / c.nf;
+    int even = (left + passes - 1) / passes;
+    while (even >= 1 && !fits(even)) even--;
     if (even >= 1 && even < c.nf) c.nf = even;
   }
   return c;
@@ -137,7 +144,7 @@ fastKronError makePlan(const Problem& pr, const PlanOptions& opt, Plan* out) {
       uint64_t Bf = B;
       if (tileOk && !inRow) Bf = B * pr.M;     // m is the fastest index: fold it into B
       if (tileOk) {
-        TileChoice tc = chooseTile(pr.dt, P, same, Bf, opt.fusion);
+        TileChoice tc = chooseTile(pr.dt, P, same, Bf, opt.fusion, opt.maxFuse);
         if (tc.nf >= 1) {
           nf = tc.nf;
           ps.kind = KernelKind::Tile;
@@ -152,6 +159,8 @@ fastKronError makePlan(const Problem& pr, const PlanOptions& opt, Plan* out) {
         const size_t es = dtypeSize(pr.dt);
         int avail = opt.fusion ? same : 1;
         if (avail > kMaxGroup) avail = kMaxGroup;
+        if (opt.maxFuse > 0 && opt.maxFuse < avail) avail = opt.maxFuse;
+        if (gMaxFuseOverride > 0 && gMaxFuseOverride < avail) avail = gMaxFuseOverride;
         for (int n = avail; n >= 1; n--) {
           if (!tileInTable(P, n, false)) continue;
           uint64_t g = 1; for (int k = 0; k < n; k++) g *= P;

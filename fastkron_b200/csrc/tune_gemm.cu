@@ -16,7 +16,7 @@
 #include "kernel_gemm.cuh"
 using namespace fkb;
 
-template <typename T, int P, int Q, int TJ, int PC, int STAGES, int MQ, int MJ, bool XT, int UNR, int MINB, bool PACK>
+template <typename T, int P, int Q, int TJ, int PC, int STAGES, int MQ, int MJ, bool XT, int UNR, int MINB, bool PACK, int ABL = 0>
 static void runVariant(const char* name, const T* X, T* Z, const T* F, unsigned long long chunks, unsigned long long B) {
   using C = GemmCfg<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT>;
   if (const char* flt = getenv("FKB_TUNE_FILTER")) if (!strstr(name, flt)) return;
@@ -26,7 +26,7 @@ static void runVariant(const char* name, const T* X, T* Z, const T* F, unsigned 
   if (XT) { a.mode = 2; a.numTiles = (chunks + TJ - 1) / TJ; a.tilesPerChunk = 1; }
   else if (B % TJ == 0) { a.mode = 0; a.tilesPerChunk = B / TJ; a.numTiles = chunks * a.tilesPerChunk; }
   else { a.mode = 1; a.tilesPerChunk = 1; a.numTiles = (chunks + TJ / B - 1) / (TJ / B); }
-  auto kern = gemmPassKernel<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT, UNR, MINB, PACK>;
+  auto kern = gemmPassKernel<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT, UNR, MINB, PACK, ABL>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM) != cudaSuccess) {
     printf("%-46s needs %zu bytes of shared memory: skipped\n", name, C::SMEM);
     cudaGetLastError();
@@ -58,6 +58,129 @@ static void runVariant(const char* name, const T* X, T* Z, const T* F, unsigned 
   printf("%-62s thr=%4d CTAs/SM=%d regs=%3d spill=%4zu smem=%6zu  %8.3f ms  %7.2f TFLOP/s  %s\n", name, C::THREADS, occ,
          fa.numRegs, (size_t)fa.localSizeBytes, C::SMEM, best, flops / best / 1e9, err == cudaSuccess ? "" : cudaGetErrorString(err));
   cudaEventDestroy(e0); cudaEventDestroy(e1);
+}
+
+// ---- experiment: the factor operand from constant memory ----------------------------------
+// A warp owns 8 rows q of the output and 32 x 8 trailing positions, so the factor value of an
+// FMA is the same for all its lanes and can come from the constant bank (a uniform load), not
+// from shared memory: the loop then reads only the X operand through the load/store unit.
+__constant__ float cFactor[64 * 64];
+
+template <int PC, int STAGES, int UNR, int MINB, int ABL>
+__global__ void __launch_bounds__(256, MINB) gemmConstF64(const GemmArgs<float> a) {
+  constexpr int P = 64, Q = 64, TJ = 256, THREADS = 256, NCH = P / PC;
+  constexpr int STAGE_ELEMS = PC * TJ;
+  extern __shared__ __align__(1024) unsigned char smemRaw[];
+  float* stages = reinterpret_cast<float*>(smemRaw);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int q0 = warp * 8;
+  const unsigned first = blockIdx.x, step = gridDim.x;
+  const unsigned numTiles = (unsigned)a.numTiles;
+  const unsigned myTiles = first < numTiles ? (numTiles - first + step - 1) / step : 0;
+  const unsigned total = myTiles * NCH;
+  const unsigned tpc = (unsigned)a.tilesPerChunk;
+  const unsigned long long PB = (unsigned long long)P * a.B, QB = (unsigned long long)Q * a.B;
+  constexpr int VPR = TJ / 4, RPP = THREADS / VPR, NLD = PC / RPP;
+  const int ldCol = (tid % VPR) * 4, ldRow = tid / VPR;
+  const unsigned long long ldOff = (unsigned long long)ldRow * a.B + ldCol;
+  const unsigned long long ldStep = (unsigned long long)RPP * a.B;
+  float* const ldSmem = stages + ldRow * TJ + ldCol;
+  unsigned isTile = first; int isC = 0; unsigned isSlot = 0;
+  auto issue = [&]() {
+    float* dst = ldSmem + (size_t)isSlot * STAGE_ELEMS;
+    const unsigned n = isTile / tpc, bt = isTile - n * tpc;
+    const float* src = a.X + n * PB + (unsigned long long)bt * TJ + (unsigned long long)isC * PC * a.B + ldOff;
+#pragma unroll
+    for (int i = 0; i < NLD; i++) { cpAsync16(dst, src); dst += RPP * TJ; src += ldStep; }
+    if (++isC == NCH) { isC = 0; isTile += step; }
+    if (++isSlot == STAGES) isSlot = 0;
+  };
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; s++) { if ((unsigned)s < total) issue(); cpAsyncCommit(); }
+  unsigned curTile = first; int c = 0; unsigned slot = 0;
+  for (unsigned s = 0; s < total; s++) {
+    cpAsyncWait<STAGES - 2>();
+    __syncthreads();
+    if (s + STAGES - 1 < total && !(ABL & 2)) issue();
+    cpAsyncCommit();
+    const float* xr = stages + (size_t)slot * STAGE_ELEMS + lane * 4;
+    const float* fr = cFactor + c * PC * Q + q0;
+#pragma unroll UNR
+    for (int pl = 0; pl < PC; pl++) {
+      const float4 xa = *reinterpret_cast<const float4*>(xr + pl * TJ);
+      const float4 xb = *reinterpret_cast<const float4*>(xr + pl * TJ + 128);
+      const float xj[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+      for (int qi = 0; qi < 8; qi++) {
+        const float f = fr[pl * Q + qi];
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[qi][j] = fmaf(f, xj[j], acc[qi][j]);
+      }
+    }
+    if (c == NCH - 1) {
+      const unsigned t = curTile;
+      const unsigned nn = t / tpc, bt = t - nn * tpc;
+      if (!(ABL & 1)) {
+        float* p0 = a.Z + nn * QB + (unsigned long long)bt * TJ + lane * 4 + (unsigned long long)q0 * a.B;
+#pragma unroll
+        for (int qi = 0; qi < 8; qi++) {
+          float* pq = p0 + (unsigned long long)qi * a.B;
+          *reinterpret_cast<float4*>(pq) = make_float4(acc[qi][0], acc[qi][1], acc[qi][2], acc[qi][3]);
+          *reinterpret_cast<float4*>(pq + 128) = make_float4(acc[qi][4], acc[qi][5], acc[qi][6], acc[qi][7]);
+        }
+      } else {
+        float sum = 0.f;
+#pragma unroll
+        for (int qi = 0; qi < 8; qi++)
+#pragma unroll
+          for (int j = 0; j < 8; j++) sum += acc[qi][j];
+        if (sum == 12345.678f) a.Z[0] = sum;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+      curTile += step;
+    }
+    if (++c == NCH) c = 0;
+    if (++slot == STAGES) slot = 0;
+  }
+  cpAsyncWait<0>();
+}
+
+template <int PC, int STAGES, int UNR, int MINB, int ABL>
+static void runConstF(const char* name, const float* X, float* Z, unsigned long long chunks, unsigned long long B) {
+  GemmArgs<float> a{};
+  a.X = X; a.Z = Z; a.numChunks = chunks; a.B = B; a.mode = 0; a.tilesPerChunk = B / 256; a.numTiles = chunks * a.tilesPerChunk;
+  auto kern = gemmConstF64<PC, STAGES, UNR, MINB, ABL>;
+  const size_t smem = (size_t)STAGES * PC * 256 * 4;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); printf("%s: smem\n", name); return; }
+  int occ = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, 256, smem);
+  if (occ < 1) { printf("%s does not fit\n", name); return; }
+  cudaFuncAttributes fa;
+  cudaFuncGetAttributes(&fa, kern);
+  unsigned long long grid = 148ull * occ;
+  if (grid > a.numTiles) grid = a.numTiles;
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0); cudaEventCreate(&e1);
+  float best = 1e9f;
+  for (int it = 0; it < 6; it++) {
+    cudaEventRecord(e0);
+    kern<<<(unsigned)grid, 256, smem>>>(a);
+    cudaEventRecord(e1); cudaEventSynchronize(e1);
+    float ms; cudaEventElapsedTime(&ms, e0, e1);
+    if (it >= 2 && ms < best) best = ms;
+  }
+  const cudaError_t err = cudaGetLastError();
+  const double flops = 2.0 * chunks * B * 64 * 64;
+  printf("%-62s thr= 256 CTAs/SM=%d regs=%3d spill=%4zu smem=%6zu  %8.3f ms  %7.2f TFLOP/s  %s\n", name, occ, fa.numRegs,
+         (size_t)fa.localSizeBytes, smem, best, flops / best / 1e9, err == cudaSuccess ? "" : cudaGetErrorString(err));
 }
 
 // ---- FFMA ceilings ---------------------------------------------------------------------
@@ -233,6 +356,44 @@ int main() {
   runProbe2<16, 8, true, 1, 128, 2>("16x8 packed, smem operands, factor stored duplicated", Z, init);
   runProbe2<8, 16, true, 1, 128, 2>("8x16 packed, smem operands, factor stored duplicated", Z, init);
   if (getenv("FKB_TUNE_PROBES_ONLY")) return 0;
+  if (getenv("FKB_TUNE_CONSTF")) {
+    printf("== 64x64 with the factor operand from constant memory\n");
+    runConstF<32, 3, 8, 2, 0>("constF PC32 S3 unroll8 minb2 complete", X, Z, ch, Bb);
+    runConstF<32, 3, 16, 2, 0>("constF PC32 S3 unroll16 minb2 complete", X, Z, ch, Bb);
+    runConstF<32, 3, 4, 2, 0>("constF PC32 S3 unroll4 minb2 complete", X, Z, ch, Bb);
+    runConstF<16, 4, 8, 2, 0>("constF PC16 S4 unroll8 minb2 complete", X, Z, ch, Bb);
+    runConstF<16, 3, 8, 3, 0>("constF PC16 S3 unroll8 minb3 complete", X, Z, ch, Bb);
+    runConstF<32, 3, 8, 2, 1>("constF PC32 S3 unroll8 minb2 no stores", X, Z, ch, Bb);
+    runConstF<32, 3, 8, 2, 2>("constF PC32 S3 unroll8 minb2 no loads", X, Z, ch, Bb);
+    runConstF<32, 3, 8, 2, 3>("constF PC32 S3 unroll8 minb2 no stores, no loads", X, Z, ch, Bb);
+    runConstF<32, 2, 8, 1, 0>("constF PC32 S2 unroll8 minb1 complete", X, Z, ch, Bb);
+    return 0;
+  }
+  if (getenv("FKB_TUNE_BIGTILE")) {
+    printf("== 64x64 with 128 accumulators per thread at three CTAs per SM\n");
+    RUN(64, 64, 256, 16, 3, 16, 8, false, 4, 3, ch, Bb);
+    RUN(64, 64, 256, 16, 3, 16, 8, false, 8, 3, ch, Bb);
+    RUN(64, 64, 256, 16, 3, 16, 8, false, 16, 3, ch, Bb);
+    RUN(64, 64, 256, 16, 4, 16, 8, false, 8, 3, ch, Bb);
+    RUN(64, 64, 256, 16, 3, 8, 16, false, 4, 3, ch, Bb);
+    RUN(64, 64, 256, 16, 3, 8, 16, false, 8, 3, ch, Bb);
+    RUN(64, 64, 256, 16, 3, 8, 16, false, 16, 3, ch, Bb);
+    RUN(64, 64, 256, 16, 4, 8, 16, false, 8, 3, ch, Bb);
+    RUN(64, 64, 256, 32, 2, 8, 16, false, 8, 2, ch, Bb);
+    RUN(64, 64, 256, 32, 2, 16, 8, false, 8, 2, ch, Bb);
+    RUN(64, 64, 512, 16, 3, 16, 8, false, 8, 1, ch, Bb);
+    RUN(64, 64, 512, 16, 3, 8, 16, false, 8, 1, ch, Bb);
+    return 0;
+  }
+  if (getenv("FKB_TUNE_ABLATE")) {
+    printf("== where the time of the 64x64 pass goes (ablations; results are wrong on purpose)\n");
+#define ABL1(PK, A, what) runVariant<float, 64, 64, 128, 32, 3, 8, 8, false, 16, 3, PK, A>("64x64 TJ128 PC32 S3 8x8 packed=" #PK " " what, X, Z, F, ch, Bb)
+    ABL1(false, 0, "complete"); ABL1(false, 1, "no stores"); ABL1(false, 2, "no loads"); ABL1(false, 4, "no barrier");
+    ABL1(false, 3, "no stores, no loads"); ABL1(false, 7, "loop only");
+    ABL1(true, 0, "complete"); ABL1(true, 1, "no stores"); ABL1(true, 2, "no loads"); ABL1(true, 4, "no barrier");
+    ABL1(true, 3, "no stores, no loads"); ABL1(true, 7, "loop only");
+    return 0;
+  }
   printf("== 64x64, trailing extent 4096 (tile mode 0)\n");
   RUN(64, 64, 128, 32, 3, 8, 8, false, 16, 3, ch, Bb);
   RUN(64, 64, 128, 32, 3, 8, 8, false, 8, 3, ch, Bb);
