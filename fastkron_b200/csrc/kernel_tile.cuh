@@ -849,6 +849,7 @@ struct TileTrArgs {
   unsigned long long mBlocks, numSuper;
   T alpha, beta;
   int epilogue;
+  int vecM;                          // the m-contiguous side may move 16-byte vectors (M and mT multiples of VEC, aligned)
 };
 
 constexpr unsigned long long kNoBase = ~0ull;
@@ -893,6 +894,20 @@ __global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tileTransposeKer
         cpAsync16Zfill(tile + physIdx<T>(idx), ok ? a.X + baseRow[r] + w : a.X, ok);
       }
       cpAsyncWaitAll();
+    } else if (a.vecM) {
+      // m-contiguous input, 16 bytes along m per access: a thread takes VEC consecutive rows at
+      // one g and scatters them into the VEC fibres (the transposition happens here)
+      const unsigned mq = (unsigned)a.mT / VEC;
+      const int items = (R / VEC) * G;
+      for (int it = threadIdx.x; it < items; it += THREADS) {
+        const unsigned q = (unsigned)it % mq, rest = (unsigned)it / mq;
+        const unsigned g = rest % G, r0 = (rest / G) * a.mT + q * VEC;
+        const bool ok = baseRow[r0] != kNoBase;
+        V x;
+        if (ok) x = *reinterpret_cast<const V*>(a.X + baseCol[r0] + (unsigned long long)g * a.M);
+#pragma unroll
+        for (int e = 0; e < VEC; e++) tile[physIdx<T>((r0 + e) * G + g)] = ok ? x.v[e] : T(0);
+      }
     } else {
       for (int v = threadIdx.x; v < nvec; v += THREADS) {
         const unsigned mi = (unsigned)v % a.mT, rest = (unsigned)v / a.mT;
@@ -910,7 +925,46 @@ __global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tileTransposeKer
     StepChain<T, P, NF, 1, THREADS, NF - 1>::run(tile, Fs, E);
 
     const bool useY = a.epilogue && a.beta != T(0) && a.Y != nullptr;
-    if (TR == 1) {
+    if (TR == 1 && a.vecM) {
+      // m-contiguous output, 16 bytes along m per access: a thread gathers one g of VEC
+      // consecutive rows from shared memory (the XOR swizzle keeps rows that are whole fibres
+      // apart in different banks) and issues one vector store; the lanes of a warp run along m
+      // first, so a warp writes whole 128-byte lines.  Y is read in batches ahead of the stores
+      // for the reason given in the pass kernel.
+      const unsigned mq = (unsigned)a.mT / VEC;
+      const int items = (R / VEC) * G;
+      constexpr int EB = 4;
+      for (int it0 = threadIdx.x; it0 < items; it0 += THREADS * EB) {
+        V y[EB];
+        unsigned long long off[EB];
+        unsigned src[EB];
+        bool ok[EB];
+#pragma unroll
+        for (int e = 0; e < EB; e++) {
+          const int it = it0 + e * THREADS;
+          ok[e] = it < items;
+          const unsigned q = (unsigned)(ok[e] ? it : it0) % mq, rest = (unsigned)(ok[e] ? it : it0) / mq;
+          const unsigned g = rest % G, r0 = (rest / G) * a.mT + q * VEC;
+          ok[e] = ok[e] && baseRow[r0] != kNoBase;
+          off[e] = baseCol[r0] + (unsigned long long)g * a.M;
+          src[e] = r0 * G + g;
+          if (ok[e] && useY) y[e] = *reinterpret_cast<const V*>(a.Y + off[e]);
+        }
+#pragma unroll
+        for (int e = 0; e < EB; e++) {
+          if (!ok[e]) continue;
+          V o;
+#pragma unroll
+          for (int i = 0; i < VEC; i++) {
+            T val = tile[physIdx<T>(src[e] + (unsigned)i * G)];
+            if (a.epilogue) val = a.alpha * val;
+            if (useY) val = fma(a.beta, y[e].v[i], val);
+            o.v[i] = val;
+          }
+          *reinterpret_cast<V*>(a.Z + off[e]) = o;
+        }
+      }
+    } else if (TR == 1) {
       for (int v = threadIdx.x; v < nvec; v += THREADS) {
         const unsigned mi = (unsigned)v % a.mT, rest = (unsigned)v / a.mT;
         const unsigned gv = rest % (G / VEC), r = (rest / (G / VEC)) * a.mT + mi;

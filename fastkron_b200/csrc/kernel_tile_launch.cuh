@@ -152,6 +152,13 @@ static fastKronError launchTileTrOne(const Pass& ps, const LaunchCtx& cx) {
   int aT = 1;
   while (aT * 2 * mT <= kTileMaxR && (size_t)aT * 2 * mT * G * es <= 32 * 1024 && (unsigned long long)aT * 2 <= ps.A) aT *= 2;
   a.mT = mT; a.aT = aT;
+  {
+    // the m-contiguous side can move 16-byte vectors when rows come in whole, aligned groups
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const void* mSide = TR == 1 ? (const void*)cx.dst : cx.src;
+    const bool yOk = TR != 1 || cx.Y == nullptr || ((uintptr_t)cx.Y & 15) == 0;
+    a.vecM = (ps.M % VEC == 0 && mT % VEC == 0 && ((uintptr_t)mSide & 15) == 0 && yOk) ? 1 : 0;
+  }
   a.mBlocks = (ps.M + mT - 1) / mT;
   a.numSuper = a.mBlocks * ((ps.A + aT - 1) / aT);
   if (a.numSuper == 0) return fastKronSuccess;

@@ -28,28 +28,35 @@ CANDIDATES = [(kb, nbuf, minb, tma)
               for (nbuf, minb) in ((2, 3), (2, 4), (1, 4), (1, 6))
               for tma in (1, 0)]
 
-# (dtype, M, factors): chosen so that the plan visits narrow and wide kernels of every table shape
+# (dtype, M, factors[, "kmm"]): chosen so that the plan visits narrow and wide kernels of every
+# table shape; "kmm" probes run Z = 2 (F (x) ...) X + Y with X stored transposed, which reaches the
+# wide kernels with m folded into the trailing index and with the beta*Y epilogue
 PROBES = [
+    ("f32", 1024, [32] * 3, "kmm"), ("f32", 1024, [16] * 4, "kmm"), ("f64", 256, [8] * 6, "kmm"),
     ("f32", 1024, [16] * 4), ("f32", 4096, [16] * 3), ("f32", 2048, [32] * 3), ("f32", 512, [8] * 6),
-    ("f32", 256, [4] * 9), ("f32", 256, [2] * 18), ("f32", 8192, [16] * 2 + [64]),
+    ("f32", 256, [4] * 9), ("f32", 256, [2] * 18), ("f32", 8192, [16] * 2 + [64]), ("f32", 256, [128, 128, 16]),
+    ("f32", 2048, [64, 64, 32]), ("f32", 4096, [64, 64, 8]),
     ("f64", 16, [8] * 8), ("f64", 512, [16] * 4), ("f64", 1024, [32] * 3), ("f64", 128, [4] * 9),
     ("f64", 128, [2] * 18), ("f64", 64, [8] * 6),
 ]
 
 
-def _plan_passes(L, dt, M, ps, max_fuse=0):
+def _plan_passes(L, dt, M, ps, kmm=False):
     buf = ctypes.create_string_buffer(1 << 16)
     from . import lib as fk
-    n = L.fkbDescribePlan(0, 1 if dt == "f64" else 0, ctypes.c_uint32(M), ctypes.c_uint32(len(ps)), fk.u32arr(ps),
-                          fk.u32arr(ps), 1, 1, 0, 1, 1, 16, buf, ctypes.c_size_t(len(buf)))
+    n = L.fkbDescribePlan(1 if kmm else 0, 1 if dt == "f64" else 0, ctypes.c_uint32(M), ctypes.c_uint32(len(ps)),
+                          fk.u32arr(ps), fk.u32arr(ps), 2 if kmm else 1, 1, 0, 1, 1, 16, buf, ctypes.c_size_t(len(buf)))
     out = []
     for ln in buf.value.decode().splitlines()[:max(n, 0)]:
         m = re.match(r"pass\d+ (\w+) f\[(\d+)\.\.(\d+)\] P=(\d+) Q=\d+ M=\d+ A=\d+ B=(\d+)", ln)
-        out.append((m.group(1), int(m.group(4)), int(m.group(3)) - int(m.group(2)) + 1, int(m.group(5)) > 1))
+        var = int(re.search(r" var=(\d+)", ln).group(1))
+        # transposing first passes (var 1/2) are a kernel family of their own: not in this table
+        out.append((m.group(1) if var == 0 else "tile-transpose", int(m.group(4)),
+                    int(m.group(3)) - int(m.group(2)) + 1, int(m.group(5)) > 1))
     return out
 
 
-def _time_passes(h, L, dt, M, ps, steps=8):
+def _time_passes(h, L, dt, M, ps, steps=8, kmm=False):
     import torch
     from . import synth
     tdt = torch.float32 if dt == "f32" else torch.float64
@@ -62,10 +69,15 @@ def _time_passes(h, L, dt, M, ps, steps=8):
     z = torch.empty(ye, dtype=tdt, device="cuda")
     t1 = torch.empty(te, dtype=tdt, device="cuda")
     t2 = torch.empty(te, dtype=tdt, device="cuda")
+    y = torch.zeros(ye, dtype=tdt, device="cuda") if kmm else None
 
     def call():
-        h.raw_gemm("mkm", "s" if dt == "f32" else "d", M, ps, ps, x.data_ptr(), 1, [f.data_ptr() for f in fs], 1,
-                   z.data_ptr(), 1.0, 0.0, 0, t1.data_ptr(), t2.data_ptr())
+        if kmm:
+            h.raw_gemm("kmm", "s" if dt == "f32" else "d", M, ps, ps, x.data_ptr(), 2, [f.data_ptr() for f in fs], 1,
+                       z.data_ptr(), 2.0, 1.0, y.data_ptr(), t1.data_ptr(), t2.data_ptr())
+        else:
+            h.raw_gemm("mkm", "s" if dt == "f32" else "d", M, ps, ps, x.data_ptr(), 1, [f.data_ptr() for f in fs], 1,
+                       z.data_ptr(), 1.0, 0.0, 0, t1.data_ptr(), t2.data_ptr())
     for _ in range(3):
         call()
     torch.cuda.synchronize()
@@ -89,38 +101,46 @@ def main():
     import fastkron_b200
     from . import lib as fk
     L = fk.get()
-    probes = PROBES[:2] + PROBES[7:8] if args.quick else PROBES
+    probes = PROBES[:4] if args.quick else PROBES
     cands = [c for c in CANDIDATES if c[0] == 32] if args.quick else CANDIDATES
-    best = {}
-    for dt, M, ps in probes:
+    samples = {}                     # (kernel key) -> {(probe id, pass index): {candidate: ms}}
+    for pi, probe in enumerate(probes):
+        dt, M, ps = probe[:3]
+        kmm = len(probe) > 3 and probe[3] == "kmm"
         for cand in cands:
             L.fkbSetTileTuning(*[ctypes.c_int(v) for v in cand])
             h = fastkron_b200.FastKron()            # a fresh handle: plans are cached per handle
-            passes = _plan_passes(L, dt, M, ps)
+            passes = _plan_passes(L, dt, M, ps, kmm)
             try:
-                times = _time_passes(h, L, dt, M, ps)
+                times = _time_passes(h, L, dt, M, ps, kmm=kmm)
             except fk.FastKronError:
                 h.close()
                 continue
             h.close()
-            for (kind, P, nf, wide), t in zip(passes, times):
+            for k, ((kind, P, nf, wide), t) in enumerate(zip(passes, times)):
                 if kind != "tile":
                     continue
                 if cand[3] == 1 and not (wide and dt == "f32" and cand[1] == 2):
                     continue                          # TMA staging exists for wide fp32 rings only
-                key = (dt, P, nf, wide)
-                cur = best.get(key)
-                rec = (t, cand, M, ps)
-                if cur is None or t < cur[0]:
-                    best[key] = rec
-                print("%s M=%d %s  %s P=%d NF=%d %s  kb=%d nbuf=%d minb=%d tma=%d  %.4f ms" % (
-                    dt, M, "x".join(map(str, ps)), kind, P, nf, "wide" if wide else "narrow", *cand, t), flush=True)
+                samples.setdefault((dt, P, nf, wide), {}).setdefault((pi, k), {})[cand] = t
+                print("%s M=%d %s%s  %s P=%d NF=%d %s  kb=%d nbuf=%d minb=%d tma=%d  %.4f ms" % (
+                    dt, M, "x".join(map(str, ps)), " kmm" if kmm else "", kind, P, nf, "wide" if wide else "narrow",
+                    *cand, t), flush=True)
     L.fkbSetTileTuning(0, 0, 0, 1)
     rows = []
-    print("\n== winners")
-    for (dt, P, nf, wide), (t, cand, M, ps) in sorted(best.items()):
-        print("%s P=%d NF=%d %-6s -> kb=%d nbuf=%d minb=%d tma=%d  (%.4f ms on M=%d %s)" % (
-            dt, P, nf, "wide" if wide else "narrow", *cand, t, M, "x".join(map(str, ps))))
+    print("\n== winners (score = mean over the probe passes that use the kernel of time / best time there)")
+    for key in sorted(samples):
+        dt, P, nf, wide = key
+        score = {}
+        for per_pass in samples[key].values():
+            lo = min(per_pass.values())
+            for cand, t in per_pass.items():
+                score.setdefault(cand, []).append(t / lo)
+        full = {c: float(np.mean(v)) for c, v in score.items() if len(v) == len(samples[key])}
+        cand = min(full, key=full.get)
+        print("%s P=%d NF=%d %-6s -> kb=%d nbuf=%d minb=%d tma=%d  (score %.3f over %d probe passes; default 32/2/3 scores %s)" % (
+            dt, P, nf, "wide" if wide else "narrow", *cand, full[cand], len(samples[key]),
+            "%.3f" % full[(32, 2, 3, 0)] if (32, 2, 3, 0) in full else "n/a"))
         rows.append("{DType::%s, %d, %d, %s, {%d, %d, %d, %d}}," % (
             "F32" if dt == "f32" else "F64", P, nf, "true" if wide else "false", *cand))
     if args.emit:
