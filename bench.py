@@ -585,6 +585,36 @@ def run_single(args):
                 "tolerance": "5e-3 of the row maximum (TF32 operands, fp32 accumulation)",
                 "timeouts": int(fk.get().fkbGemmTcTimeouts())}
 
+    # ---- shapes outside the fixed-shape kernels: the any-shape tiled kernel against the
+    # one-thread-per-output kernel it replaced (same library, same call, plan forced) --------
+    any_table = None
+    if not args.no_extra:
+        any_table = {}
+        L = fk.get()
+        for name, M, ps, qs in (("31x63^2", 4096, [31, 31], [63, 63]), ("127^2", 4096, [127, 127], [127, 127]),
+                                ("297x127", 65536, [297], [127]), ("12^4", 2048, [12] * 4, [12] * 4),
+                                ("f64 128^2", 1024, [128, 128], [128, 128])):
+            cc = dict(mm="mkm", dt="f64" if name.startswith("f64") else "f32", M=M, ps=ps, qs=qs, opx="N", opf="N",
+                      alpha=1.0, beta=0.0, seed=9, dist="uniform", name=name)
+            ent = {}
+            for label, force in (("generic", 1), ("tiled", 0)):
+                L.fkbSetForceGeneric(ctypes.c_int(force))
+                hh = fastkron_b200.FastKron()
+                rr = time_config(hh, cc, 5, 3, profile=True)
+                if label == "tiled" and not args.no_cpu:
+                    bx, bf, by, bz, bt1, bt2 = rr["buffers"]
+                    ent["parity_rows_max_rel_err"] = parity_rows(cc, bx, bf, by, bz)
+                    del bx, bf, by, bz, bt1, bt2
+                del rr["buffers"]
+                hh.close()
+                torch.cuda.empty_cache()
+                ent[label + "_gflops"] = flops_library(cc) / (rr["ms_per_step"] * 1e-3) / 1e9
+                ent[label + "_ms"] = rr["ms_per_step"]
+                ent[label + "_kernels"] = [q["kind"] for q in rr["passes"]]
+            L.fkbSetForceGeneric(ctypes.c_int(0))
+            ent["speedup"] = ent["generic_ms"] / ent["tiled_ms"]
+            any_table[name] = ent
+
     cpu = None
     if not args.no_cpu:
         cpu = cpu_whole(c, reps=2, warm=1)
@@ -597,7 +627,7 @@ def run_single(args):
         "value_harness_count": flops_harness(c) / (r["ms_per_step"] * 1e-3) / 1e9,
         "gpu_launches": r["launches"], "passes": passes, "clocks": clocks, "roofline": roof, "e2e": e2e,
         "cpu_baseline": cpu, "parity_rows_max_rel_err": parity,
-        "fma_peak_tflops": {"probe": fma_probe, "device_props": fma_props}, "configs": extra, "tf32_optin": tf32,
+        "fma_peak_tflops": {"probe": fma_probe, "device_props": fma_props}, "configs": extra, "any_shape_kernel": any_table, "tf32_optin": tf32,
         "gemm_timeouts": int(fk.get().fkbGemmTmaTimeouts()),
     }
     print(json.dumps(out))

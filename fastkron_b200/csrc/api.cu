@@ -273,6 +273,10 @@ int fkbGetPassTimes(fastKronHandle handle, float* ms, int* kinds, int maxN) {
 // this process (0 = none).  Cached plans of existing handles are not revisited.
 void fkbSetMaxFuse(int cap) { setMaxFuseOverride(cap); }
 
+// Measurement hook: while set, every plan made by this process runs all passes on the
+// one-thread-per-output kernel.  Cached plans of existing handles are not revisited.
+void fkbSetForceGeneric(int on) { setForceGenericOverride(on != 0); }
+
 // ---- introspection used by the host-side tests (not part of the reference ABI) --
 // Writes the textual plan of a problem into buf; returns the number of passes
 // or a negative fastKronError.

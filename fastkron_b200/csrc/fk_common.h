@@ -104,5 +104,7 @@ struct PlanOptions {
 fastKronError makePlan(const Problem& pr, const PlanOptions& opt, Plan* out);
 // Process-wide cap on the fusion depth (the offline tuner's hook; 0 = none).
 void setMaxFuseOverride(int cap);
+// Process-wide "every pass on the one-thread-per-output kernel" (measurement / cross-check hook).
+void setForceGenericOverride(bool on);
 
 }  // namespace fkb

@@ -24,4 +24,9 @@ inline bool gemmEligible(DType dt, uint32_t P, uint32_t Q, uint64_t B) {
   return (B % TJ == 0) || (TJ % B == 0);
 }
 
+// The any-shape large-factor kernel (kernel_gemm_any.cu) takes every single-factor pass whose
+// factor has at least 64 elements; smaller factors stay with the tile kernels or, for the few
+// shapes those do not cover, with the one-thread-per-output kernel.
+inline bool gemmAnyEligible(uint32_t P, uint32_t Q) { return (uint64_t)P * Q >= 64; }
+
 }  // namespace fkb

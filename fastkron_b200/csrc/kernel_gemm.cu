@@ -101,10 +101,24 @@ static fastKronError launchGemmOne(const Pass& ps, const LaunchCtx& cx, int mode
 // contraction layout (+4%) and 128x128, where it makes an 8x16 block per thread on a
 // 256-wide tile the best shape (+8%); the plain 64x64 pass measured the same either way
 // and stays scalar.
+static fastKronError launchGemmFixed(const Pass& ps, const LaunchCtx& cx);
+
+// The fixed-shape kernels where they apply, the any-shape kernel otherwise.
 fastKronError launchGemm(const Pass& ps, const LaunchCtx& cx) {
+  if (ps.variant != 3) {
+    const fastKronError e = launchGemmFixed(ps, cx);
+    if (e != fastKronKernelNotFound) return e;
+  }
+  return launchGemmAny(ps, cx);
+}
+
+static fastKronError launchGemmFixed(const Pass& ps, const LaunchCtx& cx) {
   if (ps.nf != 1 || ps.xsB != 1 || ps.zsB != 1) return fastKronKernelNotFound;
   const uint32_t P = ps.P[0], Q = ps.Q[0];
   if (!gemmEligible(cx.dt, P, Q, ps.B)) return fastKronKernelNotFound;
+  // dense [chunks][P][B] -> [chunks][Q][B] only
+  if (ps.xsG != (int64_t)ps.B || ps.zsG != (int64_t)ps.B || ps.xsA != (int64_t)(P * ps.B) || ps.zsA != (int64_t)(Q * ps.B)) return fastKronKernelNotFound;
+  if (ps.M > 1 && (ps.xsM != (int64_t)(ps.A * P * ps.B) || ps.zsM != (int64_t)(ps.A * Q * ps.B))) return fastKronKernelNotFound;
   if (((uintptr_t)cx.src | (uintptr_t)cx.dst | (uintptr_t)cx.Y) & 15) return fastKronKernelNotFound;
   if (cx.fsQ == 1 && (((uintptr_t)cx.F[0]) & 15)) return fastKronKernelNotFound;
   const bool xt = ps.B == 1;

@@ -46,6 +46,7 @@ fastKronError launchGeneric(const Pass& ps, const LaunchCtx& cx);
 fastKronError launchTile(const Pass& ps, const LaunchCtx& cx);
 fastKronError launchGemm(const Pass& ps, const LaunchCtx& cx);
 fastKronError launchGemmTf32(const Pass& ps, const LaunchCtx& cx);   // only reached through launchGemm
+fastKronError launchGemmAny(const Pass& ps, const LaunchCtx& cx);    // any shape, strides, alignment (through launchGemm)
 
 // True when launchTile / launchGemm have an instantiation for the pass; used
 // by the planner's caller to downgrade a pass to Generic up front.

@@ -47,6 +47,10 @@ struct TileChoice { int nf; int tileB; int tileR; };
 // process; 0 = none.
 static int gMaxFuseOverride = 0;
 void setMaxFuseOverride(int cap) { gMaxFuseOverride = cap > 0 ? cap : 0; }
+// Measurement hook: plans made while it is set use the one-thread-per-output kernel for every
+// pass (the correctness floor that the tiled kernels are compared with).
+static bool gForceGeneric = false;
+void setForceGenericOverride(bool on) { gForceGeneric = on; }
 
 // How many equal factors to fuse for the shared-memory tile kernel.  `avail` equal factors are
 // available; B is the (folded) trailing extent.  The choice is limited to the kernels that
@@ -90,7 +94,9 @@ static TileChoice chooseTile(DType dt, uint32_t P, int avail, uint64_t B, bool f
   return c;
 }
 
-fastKronError makePlan(const Problem& pr, const PlanOptions& opt, Plan* out) {
+fastKronError makePlan(const Problem& pr, const PlanOptions& optIn, Plan* out) {
+  PlanOptions opt = optIn;
+  if (gForceGeneric) opt.forceGeneric = true;
   if (!out || pr.N == 0 || pr.N > (uint32_t)kMaxFactors || pr.M == 0)
     return fastKronInvalidArgument;
   for (uint32_t i = 0; i < pr.N; i++)
@@ -127,6 +133,8 @@ fastKronError makePlan(const Problem& pr, const PlanOptions& opt, Plan* out) {
       ps.P[0] = P; ps.Q[0] = Q;
       ps.xsM = cur.ms; ps.xsA = (int64_t)P * cur.cs; ps.xsG = cur.cs; ps.xsB = cur.cs;
       ps.zsM = nxt.ms; ps.zsA = nxt.cs; ps.zsG = (int64_t)S * nxt.cs; ps.zsB = nxt.cs;
+      // the any-shape large-factor kernel takes arbitrary strides, so the rotating layout too
+      if (!opt.forceGeneric && gemmAnyEligible(P, Q)) { ps.kind = KernelKind::Gemm; ps.variant = 3; }
       cur = nxt; curCols = outCols;
     } else {
       // how many factors could share a pass with factor i
@@ -176,6 +184,12 @@ fastKronError makePlan(const Problem& pr, const PlanOptions& opt, Plan* out) {
         const uint64_t Bg = inRow ? B : B * pr.M;
         if (gemmEligible(pr.dt, P, Q, Bg)) ps.kind = KernelKind::Gemm;
       }
+      if (ps.kind == KernelKind::Generic && !opt.forceGeneric && gemmAnyEligible(P, Q)) {
+        // every other shape with a factor of 64 elements or more: the any-shape kernel (variant 3),
+        // whatever the strides, the alignment or the orientations of input and result
+        ps.kind = KernelKind::Gemm;
+        ps.variant = 3;
+      }
 
       const int f0 = i - nf + 1;
       uint64_t Pg = 1, Qg = 1;
@@ -186,7 +200,7 @@ fastKronError makePlan(const Problem& pr, const PlanOptions& opt, Plan* out) {
       ps.f0 = f0; ps.nf = nf; ps.M = pr.M; ps.A = A; ps.B = B;
       ps.xsM = cur.ms; ps.xsB = cur.cs; ps.xsG = (int64_t)B * cur.cs; ps.xsA = (int64_t)(Pg * B) * cur.cs;
       ps.zsM = nxt.ms; ps.zsB = nxt.cs; ps.zsG = (int64_t)B * nxt.cs; ps.zsA = (int64_t)(Qg * B) * nxt.cs;
-      if (ps.kind != KernelKind::Generic && ps.variant == 0 && !inRow) {
+      if (ps.kind != KernelKind::Generic && (ps.variant == 0 || ps.variant == 3) && !inRow && !outRow) {
         // folded view: [1][A][G][B*M], unit stride along the folded index
         ps.M = 1; ps.B = B * pr.M;
         ps.xsM = 0; ps.zsM = 0;

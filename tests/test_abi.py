@@ -165,9 +165,36 @@ def test_plan_fuses_benchmark_shapes(L):
     assert n == 3 and all(" tile " in ln for ln in lines), lines
     n, lines = describe(L, "mkm", "f32", 16, [8] * 8, [8] * 8, fusion=0)
     assert n == 8
-    # unaligned operands cannot use the vector kernels
+    # unaligned operands cannot use the shared-memory tile kernels; the any-shape large-factor
+    # kernel takes them (single-element accesses)
     n, lines = describe(L, "mkm", "f32", 16, [8] * 3, [8] * 3, align=4)
+    assert n == 3 and all(" gemm " in ln for ln in lines)
+    n, lines = describe(L, "mkm", "f32", 16, [4] * 3, [4] * 3, align=4)
     assert n == 3 and all(" generic " in ln for ln in lines)
+
+
+def test_no_large_factor_pass_is_left_to_the_one_thread_per_output_kernel(L):
+    """Over the reference's functional shape matrix (tests/src/general-tests-NN.cpp:34-166 of the
+    reference: 12, 24, 31, 50, 55, 127, 129, 255, 297, 31x63, 297x127, mixed shapes, all op
+    combinations, aligned or not, forward variants included) every pass whose factor has at
+    least 64 elements gets a tiled kernel."""
+    import re
+    import cases
+    seen = 0
+    for c in cases.sweep_cases():
+        for align in (16, 4):
+            for forward in (0, 1):
+                _, lines = describe(L, c["mm"], c["dt"], c["M"], c["ps"], c["qs"], c["opx"], c["opf"], forward=forward,
+                                    align=align)
+                for ln in lines:
+                    m = re.match(r"pass\d+ (\w+) f\[(\d+)\.\.(\d+)\] P=(\d+) Q=(\d+)", ln)
+                    kind, f0, f1 = m.group(1), int(m.group(2)), int(m.group(3))
+                    if kind == "generic":
+                        assert f0 == f1
+                        # KMM with one column runs as MKM: factor order is unchanged
+                        assert c["ps"][f0] * c["qs"][f0] < 64, (cases.case_id(c), ln)
+                    seen += 1
+    assert seen > 1000
 
 
 def test_plan_forward_keeps_every_intermediate(L):
