@@ -375,7 +375,22 @@ gemmPassKernel(const GemmArgs<T> a, const __grid_constant__ CUtensorMap tmap) {
       const bool useY = epi && a.beta != T(0) && a.Y != nullptr;
       // Common case first and kept short (the steady-state loop has to stay small enough
       // for the instruction cache): plain pass, no epilogue, no redistribution.
-      if ((ABL & 1) && a.numTiles != 0xFFFFFFFFull) {
+      if ((ABL & 8) && !XT) {
+        // ablation: the tile goes to a shared-memory staging area instead of global memory (what an
+        // epilogue drained by bulk tensor stores would cost the compute warps)
+        T* outS = stages + (size_t)STAGES * C::STAGE_ELEMS;
+#pragma unroll
+        for (int qi = 0; qi < MQ; qi++) {
+          T* pq = outS + ((qi / VEC) * QS + tq * VEC + (qi % VEC)) * TJ + tj * VEC;
+#pragma unroll
+          for (int g = 0; g < NGJ; g++) {
+            V o;
+#pragma unroll
+            for (int e = 0; e < VEC; e++) o.v[e] = acc.at(qi, g * VEC + e);
+            *reinterpret_cast<V*>(pq + g * JS) = o;
+          }
+        }
+      } else if ((ABL & 1) && a.numTiles != 0xFFFFFFFFull) {
         // ablation: keep the accumulators alive without storing them
         T sum = T(0);
 #pragma unroll

@@ -27,13 +27,14 @@ static void runVariant(const char* name, const T* X, T* Z, const T* F, unsigned 
   else if (B % TJ == 0) { a.mode = 0; a.tilesPerChunk = B / TJ; a.numTiles = chunks * a.tilesPerChunk; }
   else { a.mode = 1; a.tilesPerChunk = 1; a.numTiles = (chunks + TJ / B - 1) / (TJ / B); }
   auto kern = gemmPassKernel<T, P, Q, TJ, PC, STAGES, MQ, MJ, XT, UNR, MINB, PACK, ABL>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM) != cudaSuccess) {
+  const size_t SMEM_ = C::SMEM + ((ABL & 8) ? (size_t)Q * TJ * sizeof(T) : 0);
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_) != cudaSuccess) {
     printf("%-46s needs %zu bytes of shared memory: skipped\n", name, C::SMEM);
     cudaGetLastError();
     return;
   }
   int occ = 0;
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, C::THREADS, C::SMEM);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, C::THREADS, SMEM_);
   if (occ < 1) { printf("%-46s does not fit an SM\n", name); return; }
   cudaFuncAttributes fa;
   cudaFuncGetAttributes(&fa, kern);
@@ -48,7 +49,7 @@ static void runVariant(const char* name, const T* X, T* Z, const T* F, unsigned 
   float best = 1e9f;
   for (int it = 0; it < 6; it++) {
     cudaEventRecord(e0);
-    kern<<<(unsigned)grid, C::THREADS, C::SMEM>>>(a, dummyMap);
+    kern<<<(unsigned)grid, C::THREADS, SMEM_>>>(a, dummyMap);
     cudaEventRecord(e1); cudaEventSynchronize(e1);
     float ms; cudaEventElapsedTime(&ms, e0, e1);
     if (it >= 2 && ms < best) best = ms;
@@ -392,6 +393,9 @@ int main() {
     ABL1(false, 3, "no stores, no loads"); ABL1(false, 7, "loop only");
     ABL1(true, 0, "complete"); ABL1(true, 1, "no stores"); ABL1(true, 2, "no loads"); ABL1(true, 4, "no barrier");
     ABL1(true, 3, "no stores, no loads"); ABL1(true, 7, "loop only");
+#define ABL2(PK, A, what) runVariant<float, 64, 64, 128, 16, 3, 8, 8, false, 16, 3, PK, A>("64x64 TJ128 PC16 S3 8x8 packed=" #PK " " what, X, Z, F, ch, Bb)
+    ABL2(false, 0, "complete"); ABL2(false, 1, "no stores"); ABL2(false, 8, "tile to shared memory instead of global");
+    ABL2(true, 0, "complete"); ABL2(true, 1, "no stores"); ABL2(true, 8, "tile to shared memory instead of global");
     return 0;
   }
   printf("== 64x64, trailing extent 4096 (tile mode 0)\n");
