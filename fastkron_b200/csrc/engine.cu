@@ -202,7 +202,13 @@ fastKronError Engine::run(Problem pr, const CallOperands& ops) {
 
   if (pr.batch == 1) return execute(pr, plan, ops, stream_, smCount());
 
-  // Strided batch: the same plan once per entry, on offset operands.
+  // Strided batch in one launch per pass when every pass's kernel takes the batch as a grid
+  // dimension (the reference batches in grid.z, src/kernels/gpu_kmmkernel.h:124-144) ...
+  bool oneLaunch = true;
+  for (const Pass& ps : plan.passes) oneLaunch = oneLaunch && passBatchCapable(ps);
+  if (oneLaunch) return execute(pr, plan, ops, stream_, smCount(), pr.batch, tmpElems);
+
+  // ... otherwise the same plan once per entry, on offset operands.
   std::vector<const void*> fs(pr.N);
   std::vector<void*> inter(pr.N > 1 ? pr.N - 1 : 0);
   for (uint32_t b = 0; b < pr.batch; b++) {
@@ -274,7 +280,7 @@ fastKronError Engine::launchPass(const Pass& ps, const LaunchCtx& cx) {
 }
 
 fastKronError Engine::execute(const Problem& pr, const Plan& plan, const CallOperands& ops,
-                              cudaStream_t stream, int smCount) {
+                              cudaStream_t stream, int smCount, uint32_t batch, size_t tmpElems) {
   auto resolve = [&](Buf b) -> void* {
     switch (b) {
       case Buf::X:  return const_cast<void*>(ops.X);
@@ -298,6 +304,25 @@ fastKronError Engine::execute(const Problem& pr, const Plan& plan, const CallOpe
     cx.tf32 = tf32Enabled();
     for (int k = 0; k < ps.nf; k++) cx.F[k] = ops.Fs[ps.f0 + k];
     factorStrides(pr.mm, pr.opF, ps.P[0], ps.Q[0], &cx.fsP, &cx.fsQ);
+    if (batch > 1) {
+      // element distance between the batch entries of a logical buffer
+      auto strideOf = [&](Buf b) -> uint64_t {
+        switch (b) {
+          case Buf::X:  return ops.strideX;
+          case Buf::T1: case Buf::T2: return tmpElems;
+          case Buf::Z:  return ops.strideZ;
+          default: {
+            const int k = (int)b - (int)Buf::I0;
+            return ops.strideI ? ops.strideI[k] : (uint64_t)pr.M * pr.colsAfter((uint32_t)k + 1);
+          }
+        }
+      };
+      cx.batch = batch;
+      cx.bsX = strideOf(ps.src);
+      cx.bsZ = strideOf(ps.dst);
+      cx.bsY = ops.strideY;
+      for (int k = 0; k < ps.nf; k++) cx.bsF[k] = ops.strideF ? ops.strideF[ps.f0 + k] : 0;
+    }
 
     fastKronError e = launchPass(ps, cx);
     if (e != fastKronSuccess) return e;

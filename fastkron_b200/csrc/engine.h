@@ -66,9 +66,11 @@ class Engine {
   // Plan and enqueue one call on the handle's stream.
   fastKronError run(Problem pr, const CallOperands& ops);
 
-  // Enqueue the passes of `plan` for one batch entry on `stream`.
+  // Enqueue the passes of `plan` on `stream`: for one batch entry, or (batch > 1) for all
+  // entries at once, every pass one launch with the batch as a grid dimension; tmpElems is
+  // then the distance between the entries' temporaries.
   fastKronError execute(const Problem& pr, const Plan& plan, const CallOperands& ops,
-                        cudaStream_t stream, int smCount);
+                        cudaStream_t stream, int smCount, uint32_t batch = 1, size_t tmpElems = 0);
 
   float timePlan(const Problem& pr, const Plan& plan, const CallOperands& ops);
 

@@ -28,13 +28,6 @@ static EncodeTiledFn tensorMapEncoder() {
   return fn;
 }
 
-// TMA staging is on unless FASTKRON_GEMM_TMA=0.
-static bool tmaWanted() {
-  static int v = -1;
-  if (v < 0) { const char* e = getenv("FASTKRON_GEMM_TMA"); v = (e && e[0] == '0') ? 0 : 1; }
-  return v == 1;
-}
-
 // Tensor map over the pass input viewed as [chunks][P][B], box = one stage [1][PC][TJ].
 template <typename T>
 static bool encodeInputMap(CUtensorMap* tm, const void* X, unsigned long long chunks, unsigned P, unsigned long long B,
@@ -86,7 +79,7 @@ static fastKronError launchGemmOne(const Pass& ps, const LaunchCtx& cx, int mode
   CUtensorMap tmap;
   memset(&tmap, 0, sizeof(tmap));
   a.useTma = 0;
-  if (!XT && mode == 0 && a.pSplit == 0 && tmaWanted() && TJ <= 256 && PC <= 256 &&
+  if (!XT && mode == 0 && a.pSplit == 0 && TJ <= 256 && PC <= 256 &&
       encodeInputMap<T>(&tmap, a.X, a.numChunks, P, a.B, TJ, PC))
     a.useTma = 1;
   unsigned long long grid = (unsigned long long)cx.smCount * ctasPerSm;

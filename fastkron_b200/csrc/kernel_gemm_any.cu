@@ -44,6 +44,9 @@ struct AnyArgs {
   T alpha, beta;
   int epilogue;
   int vecX, vecZ, vecF;                  // 16-byte accesses allowed on X / on Z and Y / on F rows
+  // strided batch: tile index = entry * tilesPerEntry + tile within the entry (a tile never spans entries)
+  unsigned batch;
+  unsigned long long tilesPerEntry, bsX, bsZ, bsY, bsF;
 };
 
 template <int BYTES>
@@ -80,7 +83,7 @@ __device__ __forceinline__ void splitJ(const AnyArgs<T>& a, unsigned long long J
 }
 
 template <typename T, bool XT>
-__global__ void __launch_bounds__(128, 3) gemmAnyKernel(const AnyArgs<T> a) {
+__global__ void __launch_bounds__(128, 3) gemmAnyKernel(const AnyArgs<T> a0) {
   using C = AnyCfg<T>;
   using V = Vec16<T>;
   constexpr int VEC = C::VEC, TQ = C::TQ, TJ = C::TJ, PC = C::PC, MQ = C::MQ, MJ = C::MJ, THREADS = C::THREADS;
@@ -93,9 +96,18 @@ __global__ void __launch_bounds__(128, 3) gemmAnyKernel(const AnyArgs<T> a) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tq = (warp % 2) * 4 + (lane & 3);             // 8 q positions of VEC
   const int tj = (warp / 2) * 8 + (lane >> 2);            // 16 j positions of VEC
-  const unsigned nch = (a.P + PC - 1) / PC;
 
-  for (unsigned long long tile = blockIdx.x; tile < a.numTiles; tile += gridDim.x) {
+  const unsigned nch = (a0.P + PC - 1) / PC;
+  for (unsigned long long gtile = blockIdx.x; gtile < a0.numTiles; gtile += gridDim.x) {
+    // the entry's operands (a copy of the arguments with shifted pointers keeps the body unchanged)
+    AnyArgs<T> a = a0;
+    unsigned long long tile = gtile;
+    if (a0.batch > 1) {
+      const unsigned long long bt = gtile / a0.tilesPerEntry;
+      tile = gtile - bt * a0.tilesPerEntry;
+      a.X = a0.X + bt * a0.bsX; a.Z = a0.Z + bt * a0.bsZ; a.F = a0.F + bt * a0.bsF;
+      a.Y = a0.Y ? a0.Y + bt * a0.bsY : nullptr;
+    }
     const unsigned qt = (unsigned)(tile % a.qTiles);
     const unsigned long long J0 = (tile / a.qTiles) * (unsigned long long)TJ;
     const unsigned q0 = qt * TQ;
@@ -360,7 +372,9 @@ static fastKronError launchGemmAnyT(const Pass& ps, const LaunchCtx& cx) {
   a.alpha = (T)cx.alpha; a.beta = (T)cx.beta; a.epilogue = ps.epilogue ? 1 : 0;
   if (a.Jtotal == 0) return fastKronSuccess;
   a.qTiles = (a.Q + C::TQ - 1) / C::TQ;
-  a.numTiles = (unsigned long long)a.qTiles * ((a.Jtotal + C::TJ - 1) / C::TJ);
+  a.tilesPerEntry = (unsigned long long)a.qTiles * ((a.Jtotal + C::TJ - 1) / C::TJ);
+  a.batch = cx.batch; a.bsX = cx.bsX; a.bsZ = cx.bsZ; a.bsY = cx.bsY; a.bsF = cx.bsF[0];
+  a.numTiles = a.tilesPerEntry * a.batch;
 
   auto mult = [](long long v, long long m) { return v % m == 0; };
   auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
@@ -376,6 +390,11 @@ static fastKronError launchGemmAnyT(const Pass& ps, const LaunchCtx& cx) {
              (a.Y == nullptr || al16(a.Y));
   }
   a.vecF = cx.fsQ == 1 && mult((long long)a.Q, VEC) && mult(cx.fsP, VEC) && al16(a.F);
+  if (a.batch > 1) {
+    a.vecX = a.vecX && mult((long long)a.bsX, VEC);
+    a.vecZ = a.vecZ && mult((long long)a.bsZ, VEC) && mult((long long)a.bsY, VEC);
+    a.vecF = a.vecF && mult((long long)a.bsF, VEC);
+  }
 
   return xt ? launchAnyKernel<T, true>(a, cx) : launchAnyKernel<T, false>(a, cx);
 }

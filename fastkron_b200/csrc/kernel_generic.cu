@@ -35,11 +35,14 @@ struct GenericArgs {
   int epilogue;
   unsigned long long total;
   Scatter sc;
+  unsigned batch;                          // entries of a strided batch, one per blockIdx.y step
+  unsigned long long bsX, bsZ, bsY, bsF;
 };
 
 template <typename T>
 __global__ void __launch_bounds__(256) genericPassKernel(const GenericArgs<T> a) {
   const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+  for (unsigned bt = blockIdx.y; bt < a.batch; bt += gridDim.y)
   for (unsigned long long idx = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
        idx < a.total; idx += stride) {
     unsigned long long rem = idx;
@@ -55,14 +58,16 @@ __global__ void __launch_bounds__(256) genericPassKernel(const GenericArgs<T> a)
       if (k == a.d.qDim) q = c;
       coord[a.d.dimId[k]] = c;
     }
-    const T* xp = a.X + xoff;
-    const T* fp = a.F + (long long)q * a.fsQ;
+    const T* xp = a.X + (unsigned long long)bt * a.bsX + xoff;
+    const T* fp = a.F + (unsigned long long)bt * a.bsF + (long long)q * a.fsQ;
+    const T* yp = a.Y ? a.Y + (unsigned long long)bt * a.bsY : nullptr;
+    T* zp = a.Z + (unsigned long long)bt * a.bsZ;
     T acc = T(0);
     for (unsigned int p = 0; p < a.P; p++)
       acc = fma(__ldg(xp + (long long)p * a.xsP), __ldg(fp + (long long)p * a.fsP), acc);
     if (a.epilogue) {
       acc = a.alpha * acc;
-      if (a.beta != T(0) && a.Y != nullptr) acc = fma(a.beta, a.Y[zoff], acc);
+      if (a.beta != T(0) && yp != nullptr) acc = fma(a.beta, yp[zoff], acc);
     }
     if (a.sc.parts > 0) {
       // chunk index n = m*A + a of the pass; split it the way the scatter wants it
@@ -72,7 +77,7 @@ __global__ void __launch_bounds__(256) genericPassKernel(const GenericArgs<T> a)
                             (long long)(q % a.sc.qPer) * a.sc.sQ + a.sc.zOff + (long long)coord[3];
       base[off] = acc;
     } else {
-      a.Z[zoff] = acc;
+      zp[zoff] = acc;
     }
   }
 }
@@ -106,10 +111,13 @@ static fastKronError launchGenericT(const Pass& ps, const LaunchCtx& cx) {
     a.total *= ds[i].n;
   }
   if (a.total == 0) return fastKronSuccess;
+  a.batch = cx.batch; a.bsX = cx.bsX; a.bsZ = cx.bsZ; a.bsY = cx.bsY; a.bsF = cx.bsF[0];
+  if (a.sc.parts > 0 && a.batch > 1) return fastKronKernelNotFound;
   unsigned long long blocks = (a.total + 255) / 256;
   const unsigned long long cap = (unsigned long long)cx.smCount * 64;
   if (blocks > cap) blocks = cap;
-  genericPassKernel<T><<<(unsigned)blocks, 256, 0, cx.stream>>>(a);
+  const dim3 grid((unsigned)blocks, a.batch < 65535u ? a.batch : 65535u);
+  genericPassKernel<T><<<grid, 256, 0, cx.stream>>>(a);
   return cudaToFk(cudaGetLastError());
 }
 

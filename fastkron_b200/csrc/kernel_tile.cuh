@@ -43,6 +43,11 @@ struct TileArgs {
   int R;                             // sub-tiles per super-tile
   T alpha, beta;
   int epilogue;
+  // strided batch: super-tile index = entry * supersPerEntry + super-tile within the entry
+  unsigned batch;
+  unsigned long long supersPerEntry, bsX, bsZ, bsY;
+  unsigned long long bsF[kMaxGroup];
+  int batchedF;                      // some factor differs between entries: reload on entry change
 };
 
 constexpr int kTileThreads = 128;
@@ -640,11 +645,11 @@ __device__ __forceinline__ bool tileMbarWaitBounded(unsigned long long* bar, uns
   }
   return true;
 }
-// One box {BT, rows, 1} of the [chunks][G][B] view at (x = b0, y = g0, z = chunk).
-__device__ __forceinline__ void tileTmaLoad(void* smemDst, const void* tmap, int x, int y, int z, unsigned long long* bar) {
+// One box {BT, rows, 1, 1} of the [entries][chunks][G][B] view at (x = b0, y = g0, z = chunk, w = entry).
+__device__ __forceinline__ void tileTmaLoad(void* smemDst, const void* tmap, int x, int y, int z, int w, unsigned long long* bar) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
-      ::"r"((unsigned)__cvta_generic_to_shared(smemDst)), "l"(tmap), "r"(x), "r"(y), "r"(z),
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
+      ::"r"((unsigned)__cvta_generic_to_shared(smemDst)), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w),
         "r"((unsigned)__cvta_generic_to_shared(bar)) : "memory");
 }
 
@@ -693,10 +698,19 @@ tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap) {
   }
 
   const unsigned long long R = (unsigned long long)a.R;
-  const unsigned long long stride = (unsigned long long)gridDim.x * R;
+  const unsigned long long totalSupers = a.supersPerEntry * a.batch;
 
-  // Bases of the sub-tiles of the super-tile that starts at st0, and its loads into buffer b.
-  auto stage = [&](unsigned long long st0, int b) {
+  // Super-tile u of the whole (batched) launch: entry and first sub-tile within the entry.
+  auto locate = [&](unsigned long long u, unsigned long long& bt, unsigned long long& st0) {
+    bt = a.batch > 1 ? u / a.supersPerEntry : 0;
+    st0 = (u - bt * a.supersPerEntry) * R;
+  };
+
+  // Bases of the sub-tiles of super-tile u, and its loads into buffer b.
+  auto stage = [&](unsigned long long u, int b) {
+    unsigned long long bt, st0;
+    locate(u, bt, st0);
+    const T* X = a.X + bt * a.bsX;
     const unsigned long long left = a.numSub - st0;
     const int nsub = left < R ? (int)left : (int)R;
     unsigned long long* bases = basesAll + b * kTileMaxR;
@@ -706,11 +720,11 @@ tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap) {
         tileMbarExpectTx(&fullBar[b], (unsigned)(nsub * SUB * sizeof(T)));
         for (int r = 0; r < nsub; r++) {
           const unsigned long long st = st0 + r;
-          const unsigned long long chunk = st / a.tilesPerChunk, bt = st % a.tilesPerChunk;
-          bases[r] = chunk * (unsigned long long)G * a.B + bt * (unsigned long long)BT;
+          const unsigned long long chunk = st / a.tilesPerChunk, bt2 = st % a.tilesPerChunk;
+          bases[r] = chunk * (unsigned long long)G * a.B + bt2 * (unsigned long long)BT;
 #pragma unroll
           for (int g0 = 0; g0 < G; g0 += BOXR)
-            tileTmaLoad(tile + (size_t)r * SUB + (size_t)g0 * BT, &tmap, (int)(bt * BT), g0, (int)chunk, &fullBar[b]);
+            tileTmaLoad(tile + (size_t)r * SUB + (size_t)g0 * BT, &tmap, (int)(bt2 * BT), g0, (int)chunk, (int)bt, &fullBar[b]);
         }
       }
     } else {
@@ -721,8 +735,8 @@ tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap) {
         auto subBase = [&](unsigned long long st) -> unsigned long long {
           if (a.numSub <= 0xFFFFFFFFull) {
             const unsigned s32 = (unsigned)st, t32 = (unsigned)a.tilesPerChunk;
-            const unsigned c = s32 / t32, bt = s32 - c * t32;
-            return (unsigned long long)c * (unsigned long long)G * a.B + (unsigned long long)bt * BT;
+            const unsigned c = s32 / t32, bt2 = s32 - c * t32;
+            return (unsigned long long)c * (unsigned long long)G * a.B + (unsigned long long)bt2 * BT;
           }
           return (st / a.tilesPerChunk) * (unsigned long long)G * a.B + (st % a.tilesPerChunk) * (unsigned long long)BT;
         };
@@ -733,7 +747,7 @@ tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap) {
 #pragma unroll 4
             for (int j = threadIdx.x; j < VPS; j += THREADS) {
               const unsigned w = (unsigned)j * VEC;
-              cpAsync16(tile + physIdx<T, SWZ>((unsigned)r * SUB + w), a.X + base + (unsigned long long)(w / BT) * a.B + (w % BT));
+              cpAsync16(tile + physIdx<T, SWZ>((unsigned)r * SUB + w), X + base + (unsigned long long)(w / BT) * a.B + (w % BT));
             }
           }
         } else {
@@ -743,35 +757,46 @@ tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap) {
           for (int r = threadIdx.x / VPS; r < nsub; r += SPT) {
             const unsigned long long base = subBase(st0 + r);
             if (w == 0) bases[r] = base;
-            cpAsync16(tile + physIdx<T, SWZ>((unsigned)r * SUB + w), a.X + base + gw);
+            cpAsync16(tile + physIdx<T, SWZ>((unsigned)r * SUB + w), X + base + gw);
           }
         }
       } else {
         forEachTileVector<T, WIDE, SUB, BT, THREADS>(bases, st0 * G, nsub, a.B, [&](unsigned idx, unsigned long long goff) {
-          cpAsync16(tile + physIdx<T, SWZ>(idx), a.X + goff);
+          cpAsync16(tile + physIdx<T, SWZ>(idx), X + goff);
         });
       }
     }
   };
 
-  unsigned long long st0 = (unsigned long long)blockIdx.x * R;
+  unsigned long long u = blockIdx.x;
   if (NBUF == 2) {
-    if (st0 < a.numSub) stage(st0, 0);
+    if (u < totalSupers) stage(u, 0);
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   }
   unsigned phases = 0;
-  for (int it = 0; st0 < a.numSub; st0 += stride, it++) {
+  unsigned long long curEntry = 0;          // entry whose factors are in shared memory
+  for (int it = 0; u < totalSupers; u += gridDim.x, it++) {
     const int b = NBUF == 2 ? (it & 1) : 0;
+    unsigned long long bt, st0;
+    locate(u, bt, st0);
     const unsigned long long left = a.numSub - st0;
     const int nsub = left < R ? (int)left : (int)R;
     if (NBUF == 2) {
       // the other buffer's previous contents were stored before the barrier that ended the last
       // iteration: refill it now, then wait for this iteration's tile only
-      if (st0 + stride < a.numSub) stage(st0 + stride, b ^ 1);
+      if (u + gridDim.x < totalSupers) stage(u + gridDim.x, b ^ 1);
     } else {
-      stage(st0, 0);
+      stage(u, 0);
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
+    if (a.batchedF && bt != curEntry) {
+      // this entry has factors of its own (the last iteration's barrier ordered their last use)
+      for (int i = threadIdx.x; i < NF * P * P; i += THREADS) {
+        const int k = i / (P * P), p = (i / P) % P, q = i % P;
+        Fs[i] = a.F[k][bt * a.bsF[k] + (long long)p * a.fsP + (long long)q * a.fsQ];
+      }
+      curEntry = bt;
+    }
     if constexpr (TMA) {
       if (!tileMbarWaitBounded(&fullBar[b], (phases >> b) & 1u)) return;
       phases ^= 1u << b;
@@ -787,8 +812,10 @@ tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap) {
     const int E = nsub * SUB;
     StepChain<T, P, NF, BT, THREADS, NF - 1, SWZ>::run(tile, Fs, E);
 
+    T* Z = a.Z + bt * a.bsZ;
+    const T* Y = a.Y ? a.Y + bt * a.bsY : nullptr;
     const bool epi = a.epilogue != 0;
-    const bool useY = epi && a.beta != T(0) && a.Y != nullptr;
+    const bool useY = epi && a.beta != T(0) && Y != nullptr;
     if (useY) {
       // Y may be Z itself, so the compiler has to keep every read of Y ahead of the next
       // store and one vector would be in flight per thread; reading a batch of Y first keeps
@@ -802,7 +829,7 @@ tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap) {
           if (i0 + e < cnt) {
             unsigned idx; unsigned long long go;
             tileVectorAt<T, WIDE, SUB, BT, THREADS>(bases, st0 * G, a.B, i0 + e, idx, go);
-            y[e] = *reinterpret_cast<const V*>(a.Y + go);
+            y[e] = *reinterpret_cast<const V*>(Y + go);
           }
         }
 #pragma unroll
@@ -813,7 +840,7 @@ tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap) {
             V o = *reinterpret_cast<const V*>(tile + physIdx<T, SWZ>(idx));
 #pragma unroll
             for (int i = 0; i < VEC; i++) o.v[i] = fma(a.beta, y[e].v[i], a.alpha * o.v[i]);
-            *reinterpret_cast<V*>(a.Z + go) = o;
+            *reinterpret_cast<V*>(Z + go) = o;
           }
         }
       }
@@ -824,7 +851,7 @@ tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap) {
 #pragma unroll
         for (int i = 0; i < VEC; i++) o.v[i] = a.alpha * o.v[i];
       }
-      *reinterpret_cast<V*>(a.Z + goff) = o;
+      *reinterpret_cast<V*>(Z + goff) = o;
     });
     __syncthreads();
   }

@@ -32,16 +32,19 @@ inline TileEncodeFn tileMapEncoder() {
   return fn;
 }
 
-// Tensor map over a wide pass's input viewed as [chunks][G][B] fp32, box {32, min(G, 256), 1}.
-inline bool encodeTileMap(TileTmaMap* out, const void* X, unsigned long long chunks, unsigned G, unsigned long long B) {
+// Tensor map over a wide pass's input viewed as [entries][chunks][G][B] fp32 (entries of a
+// strided batch `bsX` elements apart; 1 entry otherwise), box {32, min(G, 256), 1, 1}.
+inline bool encodeTileMap(TileTmaMap* out, const void* X, unsigned long long chunks, unsigned G, unsigned long long B,
+                          unsigned batch, unsigned long long bsX) {
   static_assert(sizeof(CUtensorMap) <= sizeof(TileTmaMap), "tensor map size");
   TileEncodeFn enc = tileMapEncoder();
   if (!enc || B > 0xFFFFFFFFull || chunks > 0x7FFFFFFFull || (B * 4) % 16 != 0) return false;
-  const cuuint64_t dims[3] = {B, G, chunks};
-  const cuuint64_t strides[2] = {B * 4, (cuuint64_t)G * B * 4};
-  const cuuint32_t box[3] = {32, G < 256 ? G : 256, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  return enc(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(X), dims, strides, box,
+  if (batch > 1 && ((bsX * 4) % 16 != 0 || bsX == 0)) return false;
+  const cuuint64_t dims[4] = {B, G, chunks, batch};
+  const cuuint64_t strides[3] = {B * 4, (cuuint64_t)G * B * 4, batch > 1 ? bsX * 4 : (cuuint64_t)chunks * G * B * 4};
+  const cuuint32_t box[4] = {32, G < 256 ? G : 256, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(X), dims, strides, box,
              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -100,17 +103,22 @@ static fastKronError launchTileOne(const Pass& ps, const LaunchCtx& cx) {
   if (R < 1) R = 1;
   if (WIDE && R > kTileMaxR) R = kTileMaxR;      // wide sub-tiles keep a table of bases
   // shrunk while the grid would leave SMs idle
-  while (R > 1 && (a.numSub + R - 1) / R < (unsigned long long)cx.smCount * 3) R >>= 1;
+  while (R > 1 && ((a.numSub + R - 1) / R) * cx.batch < (unsigned long long)cx.smCount * 3) R >>= 1;
   a.R = (int)R;
 
   const size_t smem = (size_t)tn.nbuf * R * SUB * es + (size_t)NF * P * P * es + 2 * kTileMaxR * sizeof(unsigned long long);
   if (smem > 200 * 1024) return fastKronKernelNotFound;
-  const unsigned long long supers = (a.numSub + R - 1) / R;
+  a.supersPerEntry = (a.numSub + R - 1) / R;
+  a.batch = cx.batch; a.bsX = cx.bsX; a.bsZ = cx.bsZ; a.bsY = cx.bsY;
+  a.batchedF = 0;
+  for (int k = 0; k < NF; k++) { a.bsF[k] = cx.bsF[k]; if (cx.batch > 1 && cx.bsF[k] != 0) a.batchedF = 1; }
+  if (cx.batch > 1 && (((cx.bsX | cx.bsZ | cx.bsY) * es) % 16) != 0) return fastKronKernelNotFound;
+  const unsigned long long supers = a.supersPerEntry * a.batch;
   TileTmaMap tm;
   memset(&tm, 0, sizeof(tm));
   if constexpr (WIDE && sizeof(T) == 4) {
     // TMA staging needs the ring (its point is to overlap the next tile's transfer)
-    if (tn.nbuf == 2 && tn.tma && encodeTileMap(&tm, a.X, chunks, (unsigned)G, a.B)) {
+    if (tn.nbuf == 2 && tn.tma && encodeTileMap(&tm, a.X, chunks, (unsigned)G, a.B, a.batch, a.bsX)) {
       if (tn.minb >= 4) return launchTileKernel<T, P, NF, WIDE, true, 4, 2>(a, tm, smem, supers, cx);
       return launchTileKernel<T, P, NF, WIDE, true, 3, 2>(a, tm, smem, supers, cx);
     }

@@ -37,7 +37,21 @@ struct LaunchCtx {
   unsigned long long pOuter = 0, nStride = 0;
   // Gemm launcher: opt-in TF32 tensor-core kernel for fp32 passes (fastKronOptionsTF32)
   bool tf32 = false;
+  // Strided batch in ONE launch (the reference batches in grid.z, src/kernels/gpu_kmmkernel.h:124-144):
+  // entry e of `batch` reads src + e*bsX, writes dst + e*bsZ, uses Y + e*bsY and factor k at
+  // F[k] + e*bsF[k] (element strides; 0 = shared).  Honoured by the generic, any-shape and
+  // tile pass kernels (passBatchCapable); the engine loops over entries for the others.
+  uint32_t batch = 1;
+  uint64_t bsX = 0, bsZ = 0, bsY = 0;
+  uint64_t bsF[kMaxGroup] = {0};
 };
+
+// True when the kernel that runs `ps` takes a strided batch in one launch.
+inline bool passBatchCapable(const Pass& ps) {
+  if (ps.kind == KernelKind::Generic) return true;
+  if (ps.kind == KernelKind::Gemm) return ps.variant == 3;
+  return ps.kind == KernelKind::Tile && ps.variant == 0;
+}
 
 // Each returns fastKronKernelNotFound when the pass does not fit the kernel
 // family (the caller then falls back to the generic kernel), or a CUDA failure

@@ -9,8 +9,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# FASTKRON_B200_LIB selects another build of the same library (kernel experiments)
-LIB_PATH = os.environ.get("FASTKRON_B200_LIB") or os.path.join(_HERE, "libFastKron.so")
+LIB_PATH = os.path.join(_HERE, "libFastKron.so")
 
 # enum values of include/fastkron.h
 OP_N, OP_T = 1, 2

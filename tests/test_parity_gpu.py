@@ -188,6 +188,67 @@ def test_strided_batched(h, mm, share):
         assert cases.row_rel_err(zc[b].reshape(want.shape), want, mm) <= cases.TOL[dt]
 
 
+BATCH_SHAPES = [
+    # dt, M, ps, qs: tile kernels (narrow + wide, TMA ring), any-shape kernel, generic kernel, fp64 DMMA
+    ("f32", 8, [16, 16, 16, 16], [16, 16, 16, 16]),
+    ("f32", 5, [12, 31], [12, 63]),
+    ("f64", 4, [8, 8, 8, 8], [8, 8, 8, 8]),
+    ("f32", 6, [3, 5, 32, 32], [3, 5, 32, 32]),
+    ("f64", 3, [24, 9], [10, 24]),
+]
+
+
+@pytest.mark.parametrize("mm", ["mkm", "kmm"])
+@pytest.mark.parametrize("share", ["none", "x", "f"])
+@pytest.mark.parametrize("dt,M,ps,qs", BATCH_SHAPES, ids=lambda v: str(v).replace(" ", ""))
+def test_strided_batch_is_one_launch_per_pass(h, dt, M, ps, qs, mm, share):
+    """A strided batch whose passes all run on batch-capable kernels is enqueued as one launch per
+    pass (the batch is a grid dimension, as in the reference's src/kernels/gpu_kmmkernel.h:124-144),
+    with non-contiguous entries (padding between them), shared or per-entry operands."""
+    import ctypes
+    import torch
+    from fastkron_b200 import lib as fk
+    B = 4
+    ndt = cases.NP_DT[dt]
+    tdt = torch.float32 if dt == "f32" else torch.float64
+    K, Lc = int(np.prod(ps)), int(np.prod(qs))
+    pad = 64                                            # elements between entries: strides != sizes
+    rng = np.random.default_rng(17)
+    nx = 1 if share == "x" else B
+    nf = 1 if share == "f" else B
+    xs = rng.uniform(-1, 1, size=(nx, M * K + pad)).astype(ndt)
+    fss = [rng.uniform(-1, 1, size=(nf, p * q + pad)).astype(ndt) for p, q in zip(ps, qs)]
+    ys = rng.uniform(-1, 1, size=(B, M * Lc + pad)).astype(ndt)
+    xd = torch.from_numpy(xs).cuda()
+    fd = [torch.from_numpy(f).cuda() for f in fss]
+    yd = torch.from_numpy(ys).cuda()
+    ye, te = h.sizes(M, ps, qs)
+    z = torch.full((B, ye + pad), float("nan"), dtype=tdt, device="cuda")
+    t1 = torch.empty(B * te, dtype=tdt, device="cuda")
+    t2 = torch.empty(B * te, dtype=tdt, device="cuda")
+    L = fk.get()
+    L.fkbLaunchCount.restype = ctypes.c_ulonglong
+    n0 = L.fkbLaunchCount()
+    h.raw_gemm_strided_batched(mm, "s" if dt == "f32" else "d", M, ps, qs, xd.data_ptr(), 1,
+                               0 if share == "x" else M * K + pad, [f.data_ptr() for f in fd], 1,
+                               [0 if share == "f" else p * q + pad for p, q in zip(ps, qs)],
+                               z.data_ptr(), ye + pad, 2.0, 1.0, B, yd.data_ptr(), ye + pad, t1.data_ptr(), t2.data_ptr())
+    torch.cuda.synchronize()
+    launches = int(L.fkbLaunchCount() - n0)
+    buf = ctypes.create_string_buffer(1 << 14)
+    npass = L.fkbDescribePlan(ctypes.c_int(mm == "kmm"), ctypes.c_int(dt == "f64"), ctypes.c_uint32(M),
+                              ctypes.c_uint32(len(ps)), fk.u32arr(ps), fk.u32arr(qs), 1, 1, 0, 1, 1, 16, buf,
+                              ctypes.c_size_t(len(buf)))
+    assert launches == npass, (launches, npass, buf.value.decode())
+    zc = z.cpu().numpy()
+    assert np.isnan(zc[:, ye:]).all(), "the padding between result entries was written"
+    for b in range(B):
+        want = oracle.port_gekmm(mm, xs[0 if share == "x" else b][:M * K],
+                                 [f[0 if share == "f" else b][:p * q] for f, p, q in zip(fss, ps, qs)],
+                                 ps, qs, M, "N", "N", 2.0, 1.0, ys[b][:M * Lc])
+        assert cases.row_rel_err(zc[b][:ye].reshape(want.shape), want, mm) <= cases.TOL[dt]
+
+
 def test_batched_shared_factors_dense_folds_into_rows(h):
     """Strided batch with shared factors and back-to-back X/Z/Y entries (the case the reference's
     Python wrapper produces for a batched X): same result as entry-by-entry calls."""
