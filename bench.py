@@ -49,6 +49,8 @@ CONFIGS["C1s"] = dict(CONFIGS["C1"], M=64)
 CONFIGS["C5m"] = dict(CONFIGS["C5"], M=256, ps=[64] * 3, qs=[64] * 3)
 CONFIGS["C2p"] = dict(CONFIGS["C2"], M=4)
 CONFIGS["C4p"] = dict(CONFIGS["C4"], M=256)
+# the any-shape large-factor kernel on a shape outside the fixed-shape kernels (profiling / side table)
+CONFIGS["A127"] = dict(CONFIGS["C1"], M=4096, ps=[127, 127], qs=[127, 127], seed=9)
 
 
 def flops_library(c, M=None):

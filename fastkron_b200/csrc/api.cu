@@ -273,6 +273,20 @@ int fkbGetPassTimes(fastKronHandle handle, float* ms, int* kinds, int maxN) {
 // this process (0 = none).  Cached plans of existing handles are not revisited.
 void fkbSetMaxFuse(int cap) { setMaxFuseOverride(cap); }
 
+// Health check for callers of the TMA-staged kernels: every wait on a transfer barrier in this
+// library is time-bounded (about two seconds); a wait that gives up makes its CTA return without
+// writing its tiles and raises a per-device flag.  Call after synchronising the stream:
+// fastKronSuccess when no wait ever gave up on the current device, fastKronOtherError otherwise
+// (the results of the affected call are then incomplete).
+extern "C" int fkbGemmTmaTimeouts();
+extern "C" int fkbGemmTcTimeouts();
+extern "C" int fkbTileTmaTimeouts();
+fastKronError fkbDeviceStatus() {
+  const int a = fkbGemmTmaTimeouts(), b = fkbGemmTcTimeouts(), c = fkbTileTmaTimeouts();
+  if (a < 0 || b < 0 || c < 0) return fastKronBackendNotAvailable;
+  return (a | b | c) ? fastKronOtherError : fastKronSuccess;
+}
+
 // Measurement hook: while set, every plan made by this process runs all passes on the
 // one-thread-per-output kernel.  Cached plans of existing handles are not revisited.
 void fkbSetForceGeneric(int on) { setForceGenericOverride(on != 0); }

@@ -290,7 +290,12 @@ fastKronError Engine::execute(const Problem& pr, const Plan& plan, const CallOpe
       default:      return ops.intermediates ? ops.intermediates[(int)b - (int)Buf::I0] : nullptr;
     }
   };
-  for (const Pass& ps : plan.passes) {
+  // alpha = 1 without a beta*Y term is no epilogue at all: the last pass then takes the kernels'
+  // plain store path
+  const bool trivialEpilogue = ops.alpha == 1.0 && (ops.beta == 0.0 || ops.Y == nullptr);
+  for (const Pass& planned : plan.passes) {
+    Pass ps = planned;
+    if (trivialEpilogue) ps.epilogue = false;
     LaunchCtx cx;
     cx.stream = stream;
     cx.dt = pr.dt;

@@ -214,3 +214,25 @@ def test_emulated_tile_kernels_match_direct_contraction(tmp_path):
     out = subprocess.run([str(exe)], capture_output=True, text=True)
     assert out.returncode == 0, out.stdout[-2000:]
     assert "PASSED" in out.stdout
+
+
+def test_tuned_tables_name_only_instantiated_kernels():
+    """csrc/tile_db.inc / tile_fuse.inc (written by fastkron_b200/tune.py): every row names an
+    existing tile kernel and an instantiated (ring depth, CTAs per SM) pair."""
+    import re
+    csrc = os.path.join(ROOT, "fastkron_b200", "csrc")
+    table = open(os.path.join(csrc, "tile_table.h")).read()
+    narrow = set(re.findall(r"X\((\d+), (\d+)\)", table.split("#define FKB_TILE_WIDE")[0]))
+    wide = set(re.findall(r"X\((\d+), (\d+)\)", table.split("#define FKB_TILE_WIDE")[1].split("inline")[0]))
+    rows = re.findall(r"\{DType::(F32|F64), (\d+), (\d+), (true|false), \{(\d+), (\d+), (\d+), (\d+)\}\}",
+                      open(os.path.join(csrc, "tile_db.inc")).read())
+    assert len(rows) >= 20
+    for dt, P, nf, w, kb, nbuf, minb, tma in rows:
+        assert (P, nf) in (wide if w == "true" else narrow), (P, nf, w)
+        assert (int(nbuf), int(minb)) in ((2, 3), (2, 4), (1, 4), (1, 6)) and int(kb) in (16, 32, 64)
+        assert tma == "0" or (dt == "F32" and w == "true" and nbuf == "2")
+    fuse = re.findall(r"\{DType::(F32|F64), (\d+), (true|false), (\d+), (\d+)\}", open(os.path.join(csrc, "tile_fuse.inc")).read())
+    for dt, P, w, left, nf in fuse:
+        assert int(nf) <= int(left) and (P, nf) in (wide if w == "true" else narrow)
+    import fastkron_b200.tune as tune
+    assert len(tune.CANDIDATES) == 24 and len(tune.PROBES) >= 16
