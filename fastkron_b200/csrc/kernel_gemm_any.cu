@@ -93,6 +93,9 @@ __global__ void __launch_bounds__(128, 3) gemmAnyKernel(const AnyArgs<T> a0) {
   T* Xs = reinterpret_cast<T*>(smemRaw);                  // [2][XELEMS]
   T* Fs = Xs + 2 * C::XELEMS;                             // [2][FELEMS]
 
+  // [j][p] staging: input offset of row j of the tile (-1 beyond the last position), once per tile
+  __shared__ long long rowBase[XT ? TJ : 1];
+
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tq = (warp % 2) * 4 + (lane & 3);             // 8 q positions of VEC
   const int tj = (warp / 2) * 8 + (lane >> 2);            // 16 j positions of VEC
@@ -111,6 +114,20 @@ __global__ void __launch_bounds__(128, 3) gemmAnyKernel(const AnyArgs<T> a0) {
     const unsigned qt = (unsigned)(tile % a.qTiles);
     const unsigned long long J0 = (tile / a.qTiles) * (unsigned long long)TJ;
     const unsigned q0 = qt * TQ;
+    if constexpr (XT) {
+      // (the barrier that ended the previous tile's last chunk ordered the last reads of the table)
+      if (tid < TJ) {
+        const unsigned long long J = J0 + tid;
+        long long base = -1;
+        if (J < a.Jtotal) {
+          unsigned long long m, ac, b;
+          splitJ(a, J, m, ac, b);
+          base = (long long)m * a.xsM + (long long)ac * a.xsA;
+        }
+        rowBase[tid] = base;
+      }
+      __syncthreads();
+    }
 
     // ---- stage loader: chunk c of the contraction into buffer c & 1 --------------------------
     auto issue = [&](unsigned c) {
@@ -173,21 +190,18 @@ __global__ void __launch_bounds__(128, 3) gemmAnyKernel(const AnyArgs<T> a0) {
           const unsigned pl = (unsigned)(tid % VPR) * VEC;
 #pragma unroll 4
           for (int j = tid / VPR; j < TJ; j += RPP) {
-            const unsigned long long J = J0 + j;
-            const bool ok = J < a.Jtotal && p0 + pl < a.P;      // P % VEC == 0: whole vectors
-            unsigned long long m = 0, ac = 0, b = 0;
-            if (ok) splitJ(a, J, m, ac, b);
-            cpAsyncZfill<16>(xs + j * (PC + PAD) + pl, ok ? a.X + (long long)m * a.xsM + (long long)ac * a.xsA + (p0 + pl) : a.X, ok);
+            const long long base = rowBase[j];
+            const bool ok = base >= 0 && p0 + pl < a.P;         // P % VEC == 0: whole vectors
+            cpAsyncZfill<16>(xs + j * (PC + PAD) + pl, ok ? a.X + base + (p0 + pl) : a.X, ok);
           }
         } else {
           constexpr int RPP = THREADS / PC;
           const unsigned pl = (unsigned)tid % PC;
+#pragma unroll 4
           for (int j = tid / PC; j < TJ; j += RPP) {
-            const unsigned long long J = J0 + j;
-            const bool ok = J < a.Jtotal && p0 + pl < a.P;
-            unsigned long long m = 0, ac = 0, b = 0;
-            if (ok) splitJ(a, J, m, ac, b);
-            cpAsyncZfill<(int)sizeof(T)>(xs + j * (PC + PAD) + pl, ok ? a.X + (long long)m * a.xsM + (long long)ac * a.xsA + (p0 + pl) : a.X, ok);
+            const long long base = rowBase[j];
+            const bool ok = base >= 0 && p0 + pl < a.P;
+            cpAsyncZfill<(int)sizeof(T)>(xs + j * (PC + PAD) + pl, ok ? a.X + base + (p0 + pl) : a.X, ok);
           }
         }
       }
