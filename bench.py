@@ -359,10 +359,10 @@ def workload_desc(c, gpus):
 # matrix (ratio to the algorithmic bytes read), writes are the algorithmic bytes minus what
 # is still dirty in the 126 MB L2 when the kernel ends (an absolute amount, not a ratio).
 NCU_TRAFFIC = {
-    "gemm": {"read_ratio": 1.0004, "dirty_l2_bytes": 53.0e6,
-             "source": "profiles/gemm_kernel_c4_c5.md, C5m pass 3: 268.6 MB read, 215.4 MB written for 268.4 MB each way"},
-    "tile": {"read_ratio": 1.0004, "dirty_l2_bytes": 47.0e6,
-             "source": "profiles/tile_kernels_c1_c2_c3.md, C4p pass 1: 268.5 MB read, 221.4 MB written for 268.4 MB each way"},
+    "gemm": {"read_ratio": 1.0003, "dirty_l2_bytes": 52.8e6,
+             "source": "profiles/gemm_kernel_c4_c5.md, C5m passes 2-3: 268.5 MB read, 215.6 MB written for 268.4 MB each way"},
+    "tile": {"read_ratio": 1.0002, "dirty_l2_bytes": 50.4e6,
+             "source": "profiles/tile_kernels_c1_c3.md, C1 pass 2: 268.5 MB read, 218.1 MB written for 268.4 MB each way"},
 }
 
 
