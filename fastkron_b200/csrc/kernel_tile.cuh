@@ -820,7 +820,7 @@ tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap) {
       // Y may be Z itself, so the compiler has to keep every read of Y ahead of the next
       // store and one vector would be in flight per thread; reading a batch of Y first keeps
       // EB loads in flight (element i of Y is only ever needed for element i of Z).
-      constexpr int EB = sizeof(T) == 8 ? 4 : 8;
+      constexpr int EB = 4;      // more would spill registers in the contraction steps
       const int cnt = tileVectorCount<T, WIDE, SUB, THREADS>(nsub);
       for (int i0 = 0; i0 < cnt; i0 += EB) {
         V y[EB];
