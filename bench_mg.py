@@ -158,6 +158,21 @@ def run(args, CONFIGS, B):
         npass = L.fkbGetPassTimes(eng.h.h, pm, pk, 4096)
         L.fkbSetProfiling(eng.h.h, 0)
         kernel_ms = [float(pm[i]) for i in range(npass)]
+        # ... and how long the exchanges take from the moment their data is ready (staged transport)
+        exch = None
+        if eng.pipe is not None:
+            L.fkbMgPipeTrace(eng.pipe, 1)
+            eng.run(x, fs)
+            torch.cuda.synchronize()
+            tb = (ctypes.c_double * 256)()
+            ne = L.fkbMgPipeTraceGet(eng.pipe, tb, 128)
+            L.fkbMgPipeTrace(eng.pipe, 0)
+            if ne > 0:
+                ms_e = [tb[2 * i] for i in range(ne)]
+                by_e = [tb[2 * i + 1] for i in range(ne)]
+                exch = {"exchanges": ne, "ms_each": [round(v, 3) for v in ms_e], "ms_sum": float(np.sum(ms_e)),
+                        "bytes_sent_each": by_e[0], "gbs_per_exchange_mean": float(np.mean([b / (m * 1e-3) / 1e9 for b, m in zip(by_e, ms_e) if m > 0])),
+                        "note": "rank 0; from 'data ready' to the last outgoing copy's end, while the other slices compute"}
         dist.barrier()
 
         # ---- end to end: host block -> device, product, device -> host, every step ---------
@@ -167,13 +182,16 @@ def run(args, CONFIGS, B):
         torch.cuda.synchronize()
         e2e_steps = max(1, min(args.steps, 3))
         tt, copy_tt = [], []
+        # host operands want row slices whatever the transport: a slice's copies overlap the other
+        # slices' passes (the device-resident run above may use one slice, e.g. with two GPUs)
+        eng_h = eng if eng.parts >= 8 or M % 8 else mg.PipelinedRankGeMKM(M, ps, qs, parts=8, mode="auto")
         for it in range(1 + e2e_steps):
             torch.cuda.synchronize()
             dist.barrier()
             torch.cuda.synchronize()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            eng.run_host(hx, fs, hz)
+            eng_h.run_host(hx, fs, hz)
             b.record()
             torch.cuda.synchronize()
             t = torch.tensor([a.elapsed_time(b)], device="cuda")
@@ -181,6 +199,9 @@ def run(args, CONFIGS, B):
             if it > 0:
                 tt.append(float(t.item()))
         e2e_ms = float(np.mean(tt))
+        e2e_parts = eng_h.parts
+        if eng_h is not eng:
+            eng_h.close()
         # the copies alone, all ranks at once (what the host's memory system and the PCIe links give)
         xd2 = torch.empty_like(x)
         for it in range(3):
@@ -287,9 +308,10 @@ def run(args, CONFIGS, B):
             "single_call_ms": single_ms,
             "kernel_ms_one_step_rank0": {"sum": float(np.sum(kernel_ms)), "count": len(kernel_ms),
                                          "each": [round(v, 3) for v in kernel_ms[:64]]},
+            "exchange_ms_one_step_rank0": exch,
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
                     "h2d_bytes_per_step": M * Kl * 4 * world, "d2h_bytes_per_step": M * Ll * 4 * world,
-                    "ms_per_step": e2e_ms, "steps": e2e_steps, "row_slices": parts,
+                    "ms_per_step": e2e_ms, "steps": e2e_steps, "row_slices": e2e_parts,
                     "how": "each rank's pinned block: a row slice is copied in ahead of its passes and copied out when complete",
                     "h2d_alone_ms_all_ranks": h2d_alone_ms,
                     "h2d_alone_gbs_aggregate": M * Kl * 4 * world / (h2d_alone_ms * 1e-3) / 1e9,

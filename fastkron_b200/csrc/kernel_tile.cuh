@@ -48,6 +48,7 @@ struct TileArgs {
   unsigned long long supersPerEntry, bsX, bsZ, bsY;
   unsigned long long bsF[kMaxGroup];
   int batchedF;                      // some factor differs between entries: reload on entry change
+  int bulkOut;                       // TMA kernels: drain with bulk tensor stores (no epilogue arithmetic)
 };
 
 constexpr int kTileThreads = 128;
@@ -653,6 +654,13 @@ __device__ __forceinline__ void tileTmaLoad(void* smemDst, const void* tmap, int
         "r"((unsigned)__cvta_generic_to_shared(bar)) : "memory");
 }
 
+// The same box from shared memory to global memory (bulk-group completion).
+__device__ __forceinline__ void tileTmaStore(const void* tmap, int x, int y, int z, int w, const void* smemSrc) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%1, %2, %3, %4}], [%5];\n"
+      ::"l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"((unsigned)__cvta_generic_to_shared(smemSrc)) : "memory");
+}
+
 struct alignas(64) TileTmaMap { unsigned char bytes[128]; };   // a CUtensorMap, kept opaque here
 
 // The pass kernel.  Persistent CTAs walk super-tiles with a ring of two tile buffers: while the
@@ -664,10 +672,12 @@ struct alignas(64) TileTmaMap { unsigned char bytes[128]; };   // a CUtensorMap,
 //   TMA == true   wide fp32 tiles: lanes of a warp always run along the trailing index there, so
 //                 a linear [G][W] sub-tile is already free of bank conflicts and one elected
 //                 thread can stage it with cp.async.bulk.tensor (boxes of up to 256 rows of 128
-//                 bytes, completion on an mbarrier with a bounded wait)
+//                 bytes, completion on an mbarrier with a bounded wait); a pass without alpha /
+//                 beta*Y also drains its tiles with bulk tensor stores from shared memory
+//                 (a.bulkOut), so neither direction spends registers or issue slots on addresses
 template <typename T, int P, int NF, bool WIDE, bool TMA, int MINB = kTileMinBlocks, int NBUF = 2>
 __global__ void __launch_bounds__(kTileThreads, MINB)
-tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap) {
+tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap, const __grid_constant__ TileTmaMap tmapOut) {
   constexpr int THREADS = kTileThreads;
   constexpr int VEC = Vec16<T>::N;
   constexpr int BT = WIDE ? (int)(128 / sizeof(T)) : 1;
@@ -717,6 +727,8 @@ tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap) {
     T* tile = tiles + (size_t)b * tileElems;
     if constexpr (TMA) {
       if (threadIdx.x == 0) {
+        // the bulk stores that drained this buffer's previous tile must have read it
+        if (a.bulkOut) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
         tileMbarExpectTx(&fullBar[b], (unsigned)(nsub * SUB * sizeof(T)));
         for (int r = 0; r < nsub; r++) {
           const unsigned long long st = st0 + r;
@@ -816,6 +828,23 @@ tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap) {
     const T* Y = a.Y ? a.Y + bt * a.bsY : nullptr;
     const bool epi = a.epilogue != 0;
     const bool useY = epi && a.beta != T(0) && Y != nullptr;
+    if (TMA && a.bulkOut) {
+      // generic-proxy writes of the last step -> visible to the async proxy, then one thread
+      // issues the boxes (same coordinates as the loads, on the output's tensor map)
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        for (int r = 0; r < nsub; r++) {
+          const unsigned long long st = st0 + r;
+          const unsigned long long chunk = st / a.tilesPerChunk, bt2 = st % a.tilesPerChunk;
+#pragma unroll
+          for (int g0 = 0; g0 < G; g0 += BOXR)
+            tileTmaStore(&tmapOut, (int)(bt2 * BT), g0, (int)chunk, (int)bt, tile + (size_t)r * SUB + (size_t)g0 * BT);
+        }
+        asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+      }
+      continue;            // the next iteration's barrier orders the buffer's reuse by the steps
+    }
     if (useY) {
       // Y may be Z itself, so the compiler has to keep every read of Y ahead of the next
       // store and one vector would be in flight per thread; reading a batch of Y first keeps
@@ -856,6 +885,8 @@ tilePassKernel(const TileArgs<T> a, const __grid_constant__ TileTmaMap tmap) {
     __syncthreads();
   }
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+  // shared memory must stay alive until the last bulk stores have read it
+  if (TMA && a.bulkOut && threadIdx.x == 0) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
 }
 
 // ---- transposing variant ---------------------------------------------------------

@@ -50,8 +50,8 @@ inline bool encodeTileMap(TileTmaMap* out, const void* X, unsigned long long chu
 }
 
 template <typename T, int P, int NF, bool WIDE, bool TMA, int MINB = kTileMinBlocks, int NBUF = 2>
-static fastKronError launchTileKernel(const TileArgs<T>& a, const TileTmaMap& tm, size_t smem, unsigned long long supers,
-                                      const LaunchCtx& cx) {
+static fastKronError launchTileKernel(const TileArgs<T>& a, const TileTmaMap& tm, const TileTmaMap& tmOut, size_t smem,
+                                      unsigned long long supers, const LaunchCtx& cx) {
   auto kern = tilePassKernel<T, P, NF, WIDE, TMA, MINB, NBUF>;
   // per device: the shared-memory opt-in, and the occupancy for the last tile size seen
   static bool attrSetDev[kMaxDevices] = {false};
@@ -74,7 +74,7 @@ static fastKronError launchTileKernel(const TileArgs<T>& a, const TileTmaMap& tm
   const int n = occDev[dev];
   unsigned long long grid = (unsigned long long)cx.smCount * n;
   if (grid > supers) grid = supers;
-  kern<<<(unsigned)grid, kTileThreads, smem, cx.stream>>>(a, tm);
+  kern<<<(unsigned)grid, kTileThreads, smem, cx.stream>>>(a, tm, tmOut);
   return cudaToFk(cudaGetLastError());
 }
 
@@ -114,21 +114,25 @@ static fastKronError launchTileOne(const Pass& ps, const LaunchCtx& cx) {
   for (int k = 0; k < NF; k++) { a.bsF[k] = cx.bsF[k]; if (cx.batch > 1 && cx.bsF[k] != 0) a.batchedF = 1; }
   if (cx.batch > 1 && (((cx.bsX | cx.bsZ | cx.bsY) * es) % 16) != 0) return fastKronKernelNotFound;
   const unsigned long long supers = a.supersPerEntry * a.batch;
-  TileTmaMap tm;
+  TileTmaMap tm, tmOut;
   memset(&tm, 0, sizeof(tm));
+  memset(&tmOut, 0, sizeof(tmOut));
+  a.bulkOut = 0;
   if constexpr (WIDE && sizeof(T) == 4) {
     // TMA staging needs the ring (its point is to overlap the next tile's transfer)
     if (tn.nbuf == 2 && tn.tma && encodeTileMap(&tm, a.X, chunks, (unsigned)G, a.B, a.batch, a.bsX)) {
-      if (tn.minb >= 4) return launchTileKernel<T, P, NF, WIDE, true, 4, 2>(a, tm, smem, supers, cx);
-      return launchTileKernel<T, P, NF, WIDE, true, 3, 2>(a, tm, smem, supers, cx);
+      // no epilogue arithmetic: the tiles leave by bulk tensor stores as well
+      if (!a.epilogue && encodeTileMap(&tmOut, a.Z, chunks, (unsigned)G, a.B, a.batch, a.bsZ)) a.bulkOut = 1;
+      if (tn.minb >= 4) return launchTileKernel<T, P, NF, WIDE, true, 4, 2>(a, tm, tmOut, smem, supers, cx);
+      return launchTileKernel<T, P, NF, WIDE, true, 3, 2>(a, tm, tmOut, smem, supers, cx);
     }
   }
   if (tn.nbuf == 1) {
-    if (tn.minb >= 6) return launchTileKernel<T, P, NF, WIDE, false, 6, 1>(a, tm, smem, supers, cx);
-    return launchTileKernel<T, P, NF, WIDE, false, 4, 1>(a, tm, smem, supers, cx);
+    if (tn.minb >= 6) return launchTileKernel<T, P, NF, WIDE, false, 6, 1>(a, tm, tmOut, smem, supers, cx);
+    return launchTileKernel<T, P, NF, WIDE, false, 4, 1>(a, tm, tmOut, smem, supers, cx);
   }
-  if (tn.minb >= 4) return launchTileKernel<T, P, NF, WIDE, false, 4, 2>(a, tm, smem, supers, cx);
-  return launchTileKernel<T, P, NF, WIDE, false, 3, 2>(a, tm, smem, supers, cx);
+  if (tn.minb >= 4) return launchTileKernel<T, P, NF, WIDE, false, 4, 2>(a, tm, tmOut, smem, supers, cx);
+  return launchTileKernel<T, P, NF, WIDE, false, 3, 2>(a, tm, tmOut, smem, supers, cx);
 }
 
 template <typename T, bool WIDE>

@@ -273,6 +273,10 @@ struct MgPipe {
   // this rank's outgoing copies of exchange 1 / 2 done (evX1, evX2)
   std::vector<cudaEvent_t> evC2, evC3, evX1, evX2, evIn;
   uint32_t seq = 0;
+  // optional timing of the exchanges (fkbMgPipeTrace): per (phase, slice) an event when the copies
+  // may start and one per side stream when its copies of that exchange are done
+  bool trace = false;
+  std::vector<cudaEvent_t> trBegin, trEnd;     // [2][parts], [2][parts][NC]
   MgPipe* const* group = nullptr;         // one process: the pipes of this row group, by column rank
 
   size_t flagIndex(int phase, int slice, int src) const { return ((size_t)phase * parts + slice) * rank.gk + src; }
@@ -283,7 +287,7 @@ static void mgPipeDestroy(MgPipe* p) {
   int cur = 0;
   cudaGetDevice(&cur);
   cudaSetDevice(p->device);
-  for (auto* v : {&p->evC2, &p->evC3, &p->evX1, &p->evX2, &p->evIn})
+  for (auto* v : {&p->evC2, &p->evC3, &p->evX1, &p->evX2, &p->evIn, &p->trBegin, &p->trEnd})
     for (cudaEvent_t e : *v) cudaEventDestroy(e);
   for (cudaStream_t s : p->copy)
     if (s) cudaStreamDestroy(s);
@@ -435,6 +439,7 @@ static fastKronError mgEnqueueP1(MgPipe* p, int s, const float* x, const float* 
   if (err != fastKronSuccess) return err;
   if (cudaEventRecord(p->evC2[s], p->compute) != cudaSuccess) return fastKronOtherError;
   if (p->staged) {
+    if (p->trace) cudaEventRecord(p->trBegin[s], p->compute);
     for (int c = 0; c < MgPipe::NC; c++)
       if (cudaStreamWaitEvent(p->copy[c], p->evC2[s], 0) != cudaSuccess) return fastKronOtherError;
     for (int k = 1; k < G; k++) {
@@ -449,6 +454,8 @@ static fastKronError mgEnqueueP1(MgPipe* p, int s, const float* x, const float* 
     for (int k = 1; k < G; k++)
       if ((err = mgFlagTo(p, 0, s, (g + k) % G, p->compute)) != fastKronSuccess) return err;
   }
+  if (p->trace && p->staged)
+    for (int c = 0; c < MgPipe::NC; c++) cudaEventRecord(p->trEnd[(size_t)s * MgPipe::NC + c], p->copy[c]);
   return mgSignal(p, 0, s);
 }
 
@@ -466,6 +473,7 @@ static fastKronError mgEnqueueP2(MgPipe* p, int s, const float* F0) {
     err = mgPhase2Staged(p->eng, r, recvS, F0, st2);
     if (err != fastKronSuccess) return err;
     if (cudaEventRecord(p->evC3[s], p->compute) != cudaSuccess) return fastKronOtherError;
+    if (p->trace) cudaEventRecord(p->trBegin[(size_t)p->parts + s], p->compute);
     for (int c = 0; c < MgPipe::NC; c++)
       if (cudaStreamWaitEvent(p->copy[c], p->evC3[s], 0) != cudaSuccess) return fastKronOtherError;
     const size_t rows = (size_t)r.M * q1loc, width = p->B2 * sizeof(float), dpitch = (size_t)G * width;
@@ -486,6 +494,9 @@ static fastKronError mgEnqueueP2(MgPipe* p, int s, const float* F0) {
     for (int k = 1; k < G; k++)
       if ((err = mgFlagTo(p, 1, s, (g + k) % G, p->compute)) != fastKronSuccess) return err;
   }
+  if (p->trace && p->staged)
+    for (int c = 0; c < MgPipe::NC; c++)
+      cudaEventRecord(p->trEnd[((size_t)p->parts + s) * MgPipe::NC + c], p->copy[c]);
   return mgSignal(p, 1, s);
 }
 
@@ -925,6 +936,40 @@ fastKronError fkbMgPipeRunHost(void* pipe, const float* hostX, const float* cons
 }
 
 void fkbMgPipeDestroy(void* pipe) { mgPipeDestroy(reinterpret_cast<MgPipe*>(pipe)); }
+
+// Timing of the exchanges of the staged transport (measurement hook).  on != 0: the next calls
+// record, per exchange (phase, slice), when its copies may start and when each side stream has
+// finished them.  fkbMgPipeTraceGet synchronises the device and writes, for exchange e =
+// phase*parts + slice, out[2e] = milliseconds from "may start" to the last copy's end and
+// out[2e+1] = bytes this rank sent in it; returns the number of exchanges written.
+fastKronError fkbMgPipeTrace(void* pipe, int on) {
+  MgPipe* p = reinterpret_cast<MgPipe*>(pipe);
+  if (!p) return fastKronInvalidArgument;
+  if (on && p->trBegin.empty()) {
+    for (int i = 0; i < 2 * p->parts; i++) { cudaEvent_t e; if (cudaEventCreate(&e) != cudaSuccess) return fastKronOtherError; p->trBegin.push_back(e); }
+    for (int i = 0; i < 2 * p->parts * MgPipe::NC; i++) { cudaEvent_t e; if (cudaEventCreate(&e) != cudaSuccess) return fastKronOtherError; p->trEnd.push_back(e); }
+  }
+  p->trace = on != 0;
+  return fastKronSuccess;
+}
+int fkbMgPipeTraceGet(void* pipe, double* out, int maxExchanges) {
+  MgPipe* p = reinterpret_cast<MgPipe*>(pipe);
+  if (!p || !out || p->trBegin.empty() || !p->staged) return 0;
+  cudaDeviceSynchronize();
+  const int G = p->rank.gk;
+  int n = 0;
+  for (int e = 0; e < 2 * p->parts && n < maxExchanges; e++, n++) {
+    float worst = 0.f;
+    for (int c = 0; c < MgPipe::NC; c++) {
+      float ms = 0.f;
+      if (cudaEventElapsedTime(&ms, p->trBegin[e], p->trEnd[(size_t)e * MgPipe::NC + c]) != cudaSuccess) { cudaGetLastError(); ms = 0.f; }
+      if (ms > worst) worst = ms;
+    }
+    out[2 * n] = worst;
+    out[2 * n + 1] = (double)(G - 1) * (double)(e < p->parts ? p->blk1 : p->blk2) * sizeof(float);
+  }
+  return n;
+}
 
 // The two redistribution maps as plain numbers, for host-side (CPU) tests of the schedule:
 // out[0..6] = parts, qPer, aLoc, sM, sA, sQ, zOff.
