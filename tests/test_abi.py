@@ -236,3 +236,23 @@ def test_tuned_tables_name_only_instantiated_kernels():
         assert int(nf) <= int(left) and (P, nf) in (wide if w == "true" else narrow)
     import fastkron_b200.tune as tune
     assert len(tune.CANDIDATES) == 24 and len(tune.PROBES) >= 16
+
+
+def test_bench_host_logic():
+    """bench.py's workload description, operation counts and CPU-arm slab rule (no GPU needed)."""
+    sys.path.insert(0, ROOT)
+    import bench
+    c5 = dict(bench.CONFIGS["C5"], name="C5")
+    assert "factors=4x(64x64)" in bench.workload_desc(c5, 1)["workload"]
+    c4 = dict(bench.CONFIGS["C4"], name="C4")
+    assert "factors=2x(128x128),16x16" in bench.workload_desc(c4, 1)["workload"]
+    # library flop count of src/kmm/kmmalgo.h:174-184: 2*M*sum_i K_out,i * P_i
+    assert bench.flops_library(c5) == 2 * 256 * 4 * (64 ** 4) * 64
+    assert bench.flops_harness(c5) == bench.flops_library(c5) + 2 * 256 * 64 ** 4
+    # the reference counts elements in 32 bits: C5 goes to the CPU arm in slabs of 64 rows, the rest whole
+    assert bench.cpu_slab_rows(c5) == 64
+    for name in ("C1", "C2", "C3", "C4"):
+        assert bench.cpu_slab_rows(bench.CONFIGS[name]) == bench.CONFIGS[name]["M"]
+    t, src = bench.carried_traffic("gemm", 100e6 * 172, 100e6 * 172)
+    assert src.startswith("profiles/") and os.path.exists(os.path.join(ROOT, src.split(",")[0]))
+    assert 2 * 100e6 * 172 - 60e6 < t < 2 * 100e6 * 172 + 10e6
