@@ -587,6 +587,28 @@ def run_single(args):
                 "tolerance": "5e-3 of the row maximum (TF32 operands, fp32 accumulation)",
                 "timeouts": int(fk.get().fkbGemmTcTimeouts())}
 
+    # ---- opt-in split TF32 (three tensor-core products per fp32 product; fp32-level results) ----
+    tf32x3 = None
+    if not args.no_extra and c["dt"] == "f32" and c["mm"] == "mkm":
+        h3 = fastkron_b200.FastKron()
+        h3.set_options(2 | 16)                          # fastKronOptionsUseFusion | fastKronOptionsTF32x3
+        before = int(fk.get().fkbGemmTcLaunches(1))
+        rr = time_config(h3, c, max(3, min(args.steps, 5)), 3, profile=True)
+        bx, bf, by, bz, bt1, bt2 = rr["buffers"]
+        par3 = parity_rows(c, bx, bf, by, bz) if not args.no_cpu else None
+        del bx, bf, by, bz, bt1, bt2, rr["buffers"]
+        torch.cuda.empty_cache()
+        h3.close()
+        sec = rr["ms_per_step"] * 1e-3
+        slow = max(rr["passes"], key=lambda q: q["ms"]) if rr["passes"] else None
+        pass_bytes = 2 * c["M"] * int(np.prod(c["ps"], dtype=object)) * 4
+        tf32x3 = {"gflops": flops / sec / 1e9, "ms_per_step": rr["ms_per_step"], "passes": rr["passes"],
+                  "hbm_frac_slowest_pass": (pass_bytes / (slow["ms"] * 1e-3) / 1e9 / peaks.get("hbm_gbs")) if slow else None,
+                  "parity_rows_max_rel_err": par3,
+                  "tolerance": "1e-5 of the row maximum (operands split into two TF32 numbers, three products, fp32 accumulation)",
+                  "split_kernel_launches": int(fk.get().fkbGemmTcLaunches(1)) - before,
+                  "timeouts": int(fk.get().fkbGemmTcTimeouts())}
+
     # ---- shapes outside the fixed-shape kernels: the any-shape tiled kernel against the
     # one-thread-per-output kernel it replaced (same library, same call, plan forced) --------
     any_table = None
@@ -629,7 +651,7 @@ def run_single(args):
         "value_harness_count": flops_harness(c) / (r["ms_per_step"] * 1e-3) / 1e9,
         "gpu_launches": r["launches"], "passes": passes, "clocks": clocks, "roofline": roof, "e2e": e2e,
         "cpu_baseline": cpu, "parity_rows_max_rel_err": parity,
-        "fma_peak_tflops": {"probe": fma_probe, "device_props": fma_props}, "configs": extra, "any_shape_kernel": any_table, "tf32_optin": tf32,
+        "fma_peak_tflops": {"probe": fma_probe, "device_props": fma_props}, "configs": extra, "any_shape_kernel": any_table, "tf32_optin": tf32, "tf32x3_optin": tf32x3,
         "gemm_timeouts": int(fk.get().fkbGemmTmaTimeouts()),
     }
     print(json.dumps(out))

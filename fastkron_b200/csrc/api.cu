@@ -3,6 +3,7 @@
 // reference's src/fastkron.cpp:19-402 does with KMMProblem/FastKronHandle.
 
 #include "engine.h"
+#include "gemm_table.h"
 #include "fastkron.h"
 
 #include <string.h>
@@ -290,6 +291,10 @@ fastKronError fkbDeviceStatus() {
 // Measurement hook: while set, every plan made by this process runs all passes on the
 // one-thread-per-output kernel.  Cached plans of existing handles are not revisited.
 void fkbSetForceGeneric(int on) { setForceGenericOverride(on != 0); }
+
+// Measurement hook: smallest factor (elements, P*Q) that plans made afterwards give to the
+// any-shape tiled kernel instead of the one-thread-per-output kernel; 0 restores the default rule.
+void fkbSetAnyMinElems(int elems) { gAnyMinElems = elems > 0 ? elems : 0; }
 
 // ---- introspection used by the host-side tests (not part of the reference ABI) --
 // Writes the textual plan of a problem into buf; returns the number of passes

@@ -306,7 +306,7 @@ fastKronError Engine::execute(const Problem& pr, const Plan& plan, const CallOpe
     cx.alpha = ps.epilogue ? ops.alpha : 1.0;
     cx.beta = ps.epilogue ? ops.beta : 0.0;
     cx.smCount = smCount;
-    cx.tf32 = tf32Enabled();
+    cx.tf32 = tf32Mode();
     for (int k = 0; k < ps.nf; k++) cx.F[k] = ops.Fs[ps.f0 + k];
     factorStrides(pr.mm, pr.opF, ps.P[0], ps.Q[0], &cx.fsP, &cx.fsQ);
     if (batch > 1) {

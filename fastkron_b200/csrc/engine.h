@@ -53,10 +53,13 @@ class Engine {
   int device() const { return device_; }       // device that was current at initCUDA
   // SMs of the handle's device; persistent kernels size their grids from it.
   int smCount() const { return smCount_; }
-  // fastKronOptionsTF32 on the handle, or FASTKRON_TF32=1 in the environment (read once).
-  bool tf32Enabled() const {
-    static const bool env = [] { const char* e = getenv("FASTKRON_TF32"); return e && e[0] == '1'; }();
-    return env || (options_ & fastKronOptionsTF32) != 0;
+  // Tensor-core mode of fp32 large-factor passes: 3 (split TF32, fp32-level results) with
+  // fastKronOptionsTF32x3 on the handle or FASTKRON_TF32=3 in the environment, 1 (TF32 operands)
+  // with fastKronOptionsTF32 or FASTKRON_TF32=1, else 0.  The environment is read once.
+  int tf32Mode() const {
+    static const int env = [] { const char* e = getenv("FASTKRON_TF32"); return e && e[0] == '3' ? 3 : (e && e[0] == '1' ? 1 : 0); }();
+    if (env == 3 || (options_ & fastKronOptionsTF32x3) != 0) return 3;
+    return (env == 1 || (options_ & fastKronOptionsTF32) != 0) ? 1 : 0;
   }
 
   // Result / temporary element counts (per batch entry).

@@ -11,10 +11,14 @@
 //   C[q, j] = sum_p F[p, q] * X[p, j],    8 x 8 (fp32) or 8 x 4 (fp64) outputs per thread,
 // j running over the trailing positions of all chunks (so a tile may span chunks when B is
 // small) -- with everything that was a compile-time constant there a run-time value here:
-//   * the contraction runs over chunks of PC = 32 rows of p; per chunk a [PC][64] piece of the
+//   * the contraction runs over chunks of PC rows of p; per chunk a [PC][TQ] piece of the
 //     factor and a [PC][TJ] piece of X are staged in shared memory (two buffers, cp.async), rows
 //     and columns beyond P, Q or the last position zero-filled, so partial tiles need no special
 //     arithmetic;
+//   * three tile shapes, chosen by Q: 64 (q) x 128 (j) with PC = 32 for Q > 32, and 32 x 256 or
+//     16 x 256 with PC = 16 for narrower factors (a 12x12 or 16x16 factor would fill a 64-wide
+//     tile and a 32-row chunk to a few per cent; these passes are bound by HBM once the tile
+//     fits the factor);
 //   * the products of an output are accumulated over p ascending across the chunks, i.e. in the
 //     reference's order (src/kernels/cuda/mma.cuh:1-15);
 //   * global accesses are 16-byte vectors when strides and alignment allow, single elements
@@ -59,12 +63,14 @@ __device__ __forceinline__ void cpAsyncZfill(void* smemDst, const void* gmemSrc,
     asm volatile("cp.async.ca.shared.global [%0], [%1], %2, %3;\n" ::"r"(s), "l"(gmemSrc), "n"(BYTES), "r"(n) : "memory");
 }
 
-template <typename T>
+template <typename T, int TQ_>
 struct AnyCfg {
+  static_assert(TQ_ == 64 || TQ_ == 32 || TQ_ == 16, "tile heights that exist");
   static constexpr int VEC = 16 / (int)sizeof(T);
-  static constexpr int TQ = 64, MQ = 8, MJ = 2 * VEC, THREADS = 128;
-  static constexpr int TJ = (THREADS / (TQ / MQ)) * MJ;          // 128 (fp32), 64 (fp64)
-  static constexpr int PC = 32, PAD = VEC;
+  static constexpr int TQ = TQ_, MQ = (TQ_ == 16 ? 4 : 8), MJ = 2 * VEC, THREADS = 128;
+  static constexpr int WQ = TQ / MQ / 4;                         // warps along q (4 q-lanes per warp)
+  static constexpr int TJ = (THREADS / (TQ / MQ)) * MJ;          // TQ 64: 128 (fp32), 64 (fp64); else 256, 128
+  static constexpr int PC = (TQ_ == 64 ? 32 : 16), PAD = VEC;
   static constexpr int NGQ = MQ / VEC, NGJ = MJ / VEC, QS = TQ / NGQ, JS = TJ / NGJ, JT = TJ / MJ;
   static constexpr int XELEMS_N = PC * TJ, XELEMS_T = TJ * (PC + PAD);
   static constexpr int XELEMS = XELEMS_T > XELEMS_N ? XELEMS_T : XELEMS_N;
@@ -82,9 +88,9 @@ __device__ __forceinline__ void splitJ(const AnyArgs<T>& a, unsigned long long J
   ac = n - m * a.A;
 }
 
-template <typename T, bool XT>
+template <typename T, bool XT, int TQ_>
 __global__ void __launch_bounds__(128, 3) gemmAnyKernel(const AnyArgs<T> a0) {
-  using C = AnyCfg<T>;
+  using C = AnyCfg<T, TQ_>;
   using V = Vec16<T>;
   constexpr int VEC = C::VEC, TQ = C::TQ, TJ = C::TJ, PC = C::PC, MQ = C::MQ, MJ = C::MJ, THREADS = C::THREADS;
   constexpr int NGQ = C::NGQ, NGJ = C::NGJ, QS = C::QS, JS = C::JS, JT = C::JT, PAD = C::PAD;
@@ -97,8 +103,8 @@ __global__ void __launch_bounds__(128, 3) gemmAnyKernel(const AnyArgs<T> a0) {
   __shared__ long long rowBase[XT ? TJ : 1];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int tq = (warp % 2) * 4 + (lane & 3);             // 8 q positions of VEC
-  const int tj = (warp / 2) * 8 + (lane >> 2);            // 16 j positions of VEC
+  const int tq = (warp % C::WQ) * 4 + (lane & 3);         // TQ / MQ q positions
+  const int tj = (warp / C::WQ) * 8 + (lane >> 2);        // THREADS / (TQ / MQ) j positions
 
   const unsigned nch = (a0.P + PC - 1) / PC;
   for (unsigned long long gtile = blockIdx.x; gtile < a0.numTiles; gtile += gridDim.x) {
@@ -116,15 +122,15 @@ __global__ void __launch_bounds__(128, 3) gemmAnyKernel(const AnyArgs<T> a0) {
     const unsigned q0 = qt * TQ;
     if constexpr (XT) {
       // (the barrier that ended the previous tile's last chunk ordered the last reads of the table)
-      if (tid < TJ) {
-        const unsigned long long J = J0 + tid;
+      for (int r = tid; r < TJ; r += THREADS) {
+        const unsigned long long J = J0 + r;
         long long base = -1;
         if (J < a.Jtotal) {
           unsigned long long m, ac, b;
           splitJ(a, J, m, ac, b);
           base = (long long)m * a.xsM + (long long)ac * a.xsA;
         }
-        rowBase[tid] = base;
+        rowBase[r] = base;
       }
       __syncthreads();
     }
@@ -171,16 +177,17 @@ __global__ void __launch_bounds__(128, 3) gemmAnyKernel(const AnyArgs<T> a0) {
             cpAsyncZfill<16>(xs + pl * TJ + j, ok ? col + (long long)(p0 + pl) * a.xsG : a.X, ok);
           }
         } else {
-          constexpr int CPT = THREADS / TJ > 0 ? THREADS / TJ : 1;   // threads per column (fp64: 2)
-          const unsigned j = (unsigned)tid % TJ;
-          const unsigned long long J = J0 + j;
-          const bool okJ = J < a.Jtotal;
-          unsigned long long m = 0, ac = 0, b = 0;
-          if (okJ) splitJ(a, J, m, ac, b);
-          const T* col = a.X + (long long)m * a.xsM + (long long)ac * a.xsA + (long long)b * a.xsB;
-          for (int pl = tid / TJ; pl < PC; pl += CPT) {
-            const bool ok = okJ && p0 + pl < a.P;
-            cpAsyncZfill<(int)sizeof(T)>(xs + pl * TJ + j, ok ? col + (long long)(p0 + pl) * a.xsG : a.X, ok);
+          constexpr int CPT = THREADS / TJ > 0 ? THREADS / TJ : 1;   // threads per column (or columns per thread)
+          for (unsigned j = (unsigned)tid % TJ; j < (unsigned)TJ; j += THREADS) {
+            const unsigned long long J = J0 + j;
+            const bool okJ = J < a.Jtotal;
+            unsigned long long m = 0, ac = 0, b = 0;
+            if (okJ) splitJ(a, J, m, ac, b);
+            const T* col = a.X + (long long)m * a.xsM + (long long)ac * a.xsA + (long long)b * a.xsB;
+            for (int pl = tid / TJ; pl < PC; pl += CPT) {
+              const bool ok = okJ && p0 + pl < a.P;
+              cpAsyncZfill<(int)sizeof(T)>(xs + pl * TJ + j, ok ? col + (long long)(p0 + pl) * a.xsG : a.X, ok);
+            }
           }
         }
       } else {
@@ -349,10 +356,10 @@ __global__ void __launch_bounds__(128, 3) gemmAnyKernel(const AnyArgs<T> a0) {
 
 // One launcher per kernel instantiation: the shared-memory opt-in and the occupancy are
 // properties of (kernel, device).
-template <typename T, bool XT>
+template <typename T, bool XT, int TQ_>
 static fastKronError launchAnyKernel(const AnyArgs<T>& a, const LaunchCtx& cx) {
-  using C = AnyCfg<T>;
-  auto kern = gemmAnyKernel<T, XT>;
+  using C = AnyCfg<T, TQ_>;
+  auto kern = gemmAnyKernel<T, XT, TQ_>;
   static bool attrDev[kMaxDevices] = {false};
   static int occDev[kMaxDevices] = {0};
   const int dev = currentDeviceSlot();
@@ -371,9 +378,9 @@ static fastKronError launchAnyKernel(const AnyArgs<T>& a, const LaunchCtx& cx) {
   return cudaToFk(cudaGetLastError());
 }
 
-template <typename T>
+template <typename T, int TQ_>
 static fastKronError launchGemmAnyT(const Pass& ps, const LaunchCtx& cx) {
-  using C = AnyCfg<T>;
+  using C = AnyCfg<T, TQ_>;
   constexpr int VEC = C::VEC;
   AnyArgs<T> a;
   a.X = (const T*)cx.src; a.Z = (T*)cx.dst; a.Y = (const T*)cx.Y; a.F = (const T*)cx.F[0];
@@ -410,16 +417,25 @@ static fastKronError launchGemmAnyT(const Pass& ps, const LaunchCtx& cx) {
     a.vecF = a.vecF && mult((long long)a.bsF, VEC);
   }
 
-  return xt ? launchAnyKernel<T, true>(a, cx) : launchAnyKernel<T, false>(a, cx);
+  return xt ? launchAnyKernel<T, true, TQ_>(a, cx) : launchAnyKernel<T, false, TQ_>(a, cx);
 }
 
-// Any single-factor pass with P*Q >= 64 whose operands are plain strided tensors (no
+// Tile height by factor width: the narrowest tile that holds all of Q (up to 64).
+template <typename T>
+static fastKronError launchGemmAnyQ(const Pass& ps, const LaunchCtx& cx) {
+  const uint32_t Q = ps.Q[0];
+  if (Q <= 16) return launchGemmAnyT<T, 16>(ps, cx);
+  if (Q <= 32) return launchGemmAnyT<T, 32>(ps, cx);
+  return launchGemmAnyT<T, 64>(ps, cx);
+}
+
+// Any single-factor pass the eligibility rule (gemm_table.h) admits whose operands are plain strided tensors (no
 // redistribution over GPUs, no split input).
 fastKronError launchGemmAny(const Pass& ps, const LaunchCtx& cx) {
   if (ps.nf != 1 || cx.scatter.parts > 0 || cx.pSplit != 0) return fastKronKernelNotFound;
   if (!gemmAnyEligible(ps.P[0], ps.Q[0])) return fastKronKernelNotFound;
-  if (cx.dt == DType::F32) return launchGemmAnyT<float>(ps, cx);
-  return launchGemmAnyT<double>(ps, cx);
+  if (cx.dt == DType::F32) return launchGemmAnyQ<float>(ps, cx);
+  return launchGemmAnyQ<double>(ps, cx);
 }
 
 }  // namespace fkb

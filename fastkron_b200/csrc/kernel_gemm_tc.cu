@@ -22,6 +22,16 @@
 // the next.  Every barrier wait is time-bounded; a wait that gives up raises an abort flag
 // that ends all role loops, TMEM is released on every path, and the host sees
 // fkbGemmTcTimeouts() != 0.  No cluster launch, no multicast.
+//
+// SPLIT variant (fastKronOptionsTF32x3 / FASTKRON_TF32=3; 64x64 factors): every fp32 operand is
+// split into two TF32 numbers, hi = rna_tf32(v) and lo = rna_tf32(v - hi), and a product is
+// formed as lo*hi + hi*lo + hi*hi on the tensor cores with fp32 accumulation (the dropped lo*lo
+// term and the rounding of lo are of relative size 2^-21): results agree with the fp32 kernels to
+// about 1e-6 of the row maximum, i.e. well inside the fp32 tolerance of the default path, at
+// three times the tensor-core work, which still leaves the pass bound by HBM.  The factor is
+// split once per CTA into two shared-memory copies; four more warps ("converters", 320 threads
+// in all) split each X stage in place (hi) and into a second buffer of the stage (lo) between
+// its arrival and its MMAs, and hand it over through one more mbarrier per stage.
 #include <cuda.h>
 #include <string.h>
 #include <stdlib.h>
@@ -36,7 +46,15 @@ __device__ int gGemmTcTimeouts = 0;
 namespace tc {
 
 constexpr int kThreads = 192;
+constexpr int kConvThreads = 128;                  // SPLIT: four converter warps after the six role warps
 constexpr int kRows = 128;                         // MMA M: rows of (n, j) per tile
+
+// v as a TF32 number (round to nearest, ties away; the low 13 mantissa bits come back zero)
+__device__ __forceinline__ float tf32Round(float v) {
+  unsigned u;
+  asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(u) : "f"(v));
+  return __uint_as_float(u);
+}
 
 struct Args {
   float* Z; const float* Y; const float* F;
@@ -135,21 +153,30 @@ __device__ __forceinline__ void tmemLoadWait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void fenceBeforeSync() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void fenceAfterSync() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 
-// P = Q.  XT: trailing extent 1 (contraction index contiguous in X).
-template <int P, bool XT>
-__global__ void __launch_bounds__(kThreads, 1)
+// Stages of the X ring.  SPLIT stages are twice as large (hi and lo copies).
+__host__ __device__ constexpr int stagesOf(int P, bool XT, bool SPLIT) {
+  return SPLIT ? (XT ? 2 : 3) : (P == 64 ? 4 : 2);
+}
+
+// P = Q.  XT: trailing extent 1 (contraction index contiguous in X).  SPLIT: three TF32 products
+// per fp32 product (see the head of the file).
+template <int P, bool XT, bool SPLIT>
+__global__ void __launch_bounds__(SPLIT ? kThreads + kConvThreads : kThreads, 1)
 gemmTf32Kernel(const Args a, const __grid_constant__ CUtensorMap tmX) {
+  static_assert(!SPLIT || P == 64, "the split variant exists for 64x64 factors");
   constexpr int Q = P;
-  constexpr int NS = P == 64 ? 4 : 2;                       // stages of the X ring
+  constexpr int NS = stagesOf(P, XT, SPLIT);                // stages of the X ring
   constexpr unsigned kStageBytes = (unsigned)P * kRows * 4u;
+  constexpr unsigned kStageStride = SPLIT ? 2u * kStageBytes : kStageBytes;   // SPLIT: [hi][lo]
+  constexpr unsigned kFactorBytes = (unsigned)P * Q * 4u;
   constexpr unsigned kAtomBytes = (unsigned)P * 128u;        // one [P][32 floats] atom column of an MN-major operand
   constexpr int kCols = 2 * Q;                              // TMEM columns: two accumulators
 
   extern __shared__ unsigned char smemRaw[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);
-  unsigned char* Fs = base;                                 // [Q/32][P][32] floats, swizzled
-  unsigned char* stages = base + (size_t)P * Q * 4;
-  __shared__ __align__(8) unsigned long long fullBar[NS], emptyBar[NS], accFull[2], accEmpty[2];
+  unsigned char* Fs = base;                                 // [Q/32][P][32] floats, swizzled (SPLIT: hi, then lo)
+  unsigned char* stages = base + (size_t)kFactorBytes * (SPLIT ? 2 : 1);
+  __shared__ __align__(8) unsigned long long fullBar[NS], emptyBar[NS], convBar[NS], accFull[2], accEmpty[2];
   __shared__ unsigned tmemBaseSlot;
   __shared__ int abortFlag;
   // XT epilogue: a thread holds 32 consecutive q of one chunk, but a coalesced store wants 32
@@ -160,7 +187,7 @@ gemmTf32Kernel(const Args a, const __grid_constant__ CUtensorMap tmX) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   if (tid == 0) {
-    for (int i = 0; i < NS; i++) { mbarInit(&fullBar[i], 1); mbarInit(&emptyBar[i], 1); }
+    for (int i = 0; i < NS; i++) { mbarInit(&fullBar[i], 1); mbarInit(&emptyBar[i], 1); mbarInit(&convBar[i], kConvThreads / 32); }
     for (int i = 0; i < 2; i++) { mbarInit(&accFull[i], 1); mbarInit(&accEmpty[i], 4); }
     abortFlag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -171,13 +198,19 @@ gemmTf32Kernel(const Args a, const __grid_constant__ CUtensorMap tmX) {
   }
   // factor -> shared memory: element (p, q) of atom column q / 32 sits in row p, 32-byte unit
   // ((q % 32) / 8) ^ (p % 4): the 128-byte swizzle with 32-byte atoms.
-  for (int i = tid; i < P * Q; i += kThreads) {
+  for (int i = tid; i < P * Q; i += (int)blockDim.x) {
     int p, q;
     if (a.fsQ == 1) { p = i / Q; q = i % Q; } else { q = i / P; p = i % P; }     // walk the stored order
     const float v = a.F[(long long)p * a.fsP + (long long)q * a.fsQ];
     const unsigned off = (unsigned)(q >> 5) * kAtomBytes + (unsigned)p * 128u + ((((unsigned)(q & 31) >> 3) ^ ((unsigned)p & 3u)) << 5) +
                          ((unsigned)q & 7u) * 4u;
-    *reinterpret_cast<float*>(Fs + off) = v;
+    if constexpr (SPLIT) {
+      const float hi = tf32Round(v);
+      *reinterpret_cast<float*>(Fs + off) = hi;
+      *reinterpret_cast<float*>(Fs + kFactorBytes + off) = tf32Round(v - hi);
+    } else {
+      *reinterpret_cast<float*>(Fs + off) = v;
+    }
   }
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // generic-proxy writes -> tensor-core reads
   fenceBeforeSync();
@@ -197,7 +230,7 @@ gemmTf32Kernel(const Args a, const __grid_constant__ CUtensorMap tmX) {
         const unsigned s = it % NS, ph = (it / NS) & 1u;
         if (!waitBounded(&emptyBar[s], ph ^ 1u, abortP)) break;
         mbarExpectTx(&fullBar[s], kStageBytes);
-        unsigned char* dst = stages + (size_t)s * kStageBytes;
+        unsigned char* dst = stages + (size_t)s * kStageStride;
         if constexpr (!XT) {
           // four atoms of [P][32 j]; one whose chunk lies past the end is zero-filled by the TMA
           unsigned n0, j0, atomsPerChunk;
@@ -221,23 +254,57 @@ gemmTf32Kernel(const Args a, const __grid_constant__ CUtensorMap tmX) {
       for (unsigned it = 0; it < myTiles && !*abortP; it++) {
         const unsigned s = it % NS, ph = (it / NS) & 1u;
         const unsigned acc = it & 1u, aph = (it >> 1) & 1u;
-        if (!waitBounded(&fullBar[s], ph, abortP)) break;
+        // SPLIT: the converters hand the stage over (they waited for its arrival themselves)
+        if (!waitBounded(SPLIT ? &convBar[s] : &fullBar[s], ph, abortP)) break;
         if (!waitBounded(&accEmpty[acc], aph ^ 1u, abortP)) break;
         fenceAfterSync();
-        const unsigned stageAddr = smemAddr(stages + (size_t)s * kStageBytes);
+        const unsigned stageAddr = smemAddr(stages + (size_t)s * kStageStride);
         const unsigned fAddr = smemAddr(Fs);
         const unsigned tmemD = tmemBase + acc * (unsigned)Q;
+        // one sweep over the contraction index: A operand at xAddr, factor copy at fBase
+        auto sweep = [&](unsigned xAddr, unsigned fBase, bool fresh) {
 #pragma unroll
-        for (int ks = 0; ks < P / 8; ks++) {
-          unsigned long long ad, bd;
-          if constexpr (!XT) ad = smemDesc(stageAddr + (unsigned)ks * 1024u, kAtomBytes, 512u, kSwz128Atom32);
-          else ad = smemDesc(stageAddr + (unsigned)(ks / 4) * (kRows * 128u) + (unsigned)(ks % 4) * 32u, 16u, 1024u, kSwz128);
-          bd = smemDesc(fAddr + (unsigned)ks * 1024u, kAtomBytes, 512u, kSwz128Atom32);
-          mmaTf32(tmemD, ad, bd, idesc, ks > 0 ? 1u : 0u);
+          for (int ks = 0; ks < P / 8; ks++) {
+            unsigned long long ad, bd;
+            if constexpr (!XT) ad = smemDesc(xAddr + (unsigned)ks * 1024u, kAtomBytes, 512u, kSwz128Atom32);
+            else ad = smemDesc(xAddr + (unsigned)(ks / 4) * (kRows * 128u) + (unsigned)(ks % 4) * 32u, 16u, 1024u, kSwz128);
+            bd = smemDesc(fBase + (unsigned)ks * 1024u, kAtomBytes, 512u, kSwz128Atom32);
+            mmaTf32(tmemD, ad, bd, idesc, (ks > 0 || !fresh) ? 1u : 0u);
+          }
+        };
+        if constexpr (SPLIT) {
+          sweep(stageAddr + kStageBytes, fAddr, true);              // lo * hi   (small terms first)
+          sweep(stageAddr, fAddr + kFactorBytes, false);            // hi * lo
+          sweep(stageAddr, fAddr, false);                           // hi * hi
+        } else {
+          sweep(stageAddr, fAddr, true);
         }
         mmaCommit(&emptyBar[s]);        // stage reusable once these MMAs have read it
         mmaCommit(&accFull[acc]);       // accumulator complete
       }
+    }
+  } else if (SPLIT && warp >= kThreads / 32) {
+    // ---- converters (SPLIT): stage -> hi in place, lo behind it -------------------------------
+    const int ct = tid - kThreads;
+    for (unsigned it = 0; it < myTiles; it++) {
+      const unsigned s = it % NS, ph = (it / NS) & 1u;
+      bool ok = !*abortP && waitBounded(&fullBar[s], ph, abortP);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      float4* hiP = reinterpret_cast<float4*>(stages + (size_t)s * kStageStride);
+      float4* loP = reinterpret_cast<float4*>(stages + (size_t)s * kStageStride + kStageBytes);
+#pragma unroll 4
+      for (int i = ct; i < (int)(kStageBytes / 16); i += kConvThreads) {
+        const float4 v = hiP[i];
+        float4 h, l;
+        h.x = tf32Round(v.x); h.y = tf32Round(v.y); h.z = tf32Round(v.z); h.w = tf32Round(v.w);
+        l.x = tf32Round(v.x - h.x); l.y = tf32Round(v.y - h.y); l.z = tf32Round(v.z - h.z); l.w = tf32Round(v.w - h.w);
+        hiP[i] = h;
+        loP[i] = l;
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // these writes -> tensor-core reads
+      __syncwarp();
+      if (lane == 0) mbarArrive(&convBar[s]);
     }
   } else {
     // ---- epilogue: warp w reads TMEM lanes [32*(w%4), +32) ---------------------------------
@@ -318,6 +385,9 @@ gemmTf32Kernel(const Args a, const __grid_constant__ CUtensorMap tmX) {
   }
 }
 
+// launches of the plain / split kernels by this process (tests check that the opt-in took effect)
+static unsigned long long gLaunches[2] = {0, 0};
+
 // cuTensorMapEncodeTiled from the driver, without linking libcuda.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -338,9 +408,9 @@ static EncodeTiledFn encoder() {
   return fn;
 }
 
-template <int P, bool XT>
+template <int P, bool XT, bool SPLIT>
 static fastKronError launchOne(const Pass& ps, const LaunchCtx& cx) {
-  constexpr int NS = P == 64 ? 4 : 2;
+  constexpr int NS = stagesOf(P, XT, SPLIT);
   const unsigned long long chunks = ps.M * ps.A, B = ps.B;
   EncodeTiledFn enc = encoder();
   if (!enc || chunks == 0 || chunks > 0x7FFFFFFFull || B > 0x7FFFFFFFull) return fastKronKernelNotFound;
@@ -384,8 +454,8 @@ static fastKronError launchOne(const Pass& ps, const LaunchCtx& cx) {
   if (tiles >= (1ull << 31)) return fastKronKernelNotFound;
   a.numTiles = (unsigned)tiles;
 
-  const size_t smem = (size_t)P * P * 4 + (size_t)NS * P * kRows * 4 + 1024;
-  auto kern = gemmTf32Kernel<P, XT>;
+  const size_t smem = ((size_t)P * P * 4 + (size_t)NS * P * kRows * 4) * (SPLIT ? 2 : 1) + 1024;
+  auto kern = gemmTf32Kernel<P, XT, SPLIT>;
   static bool attrDev[kMaxDevices] = {false};
   bool& attr = attrDev[currentDeviceSlot()];
   if (!attr) {
@@ -395,7 +465,8 @@ static fastKronError launchOne(const Pass& ps, const LaunchCtx& cx) {
   }
   unsigned grid = (unsigned)cx.smCount;
   if (grid > a.numTiles) grid = a.numTiles;
-  kern<<<grid, kThreads, smem, cx.stream>>>(a, tm);
+  kern<<<grid, SPLIT ? kThreads + kConvThreads : kThreads, smem, cx.stream>>>(a, tm);
+  gLaunches[SPLIT ? 1 : 0]++;
   return cudaToFk(cudaGetLastError());
 }
 
@@ -413,9 +484,16 @@ fastKronError launchGemmTf32(const Pass& ps, const LaunchCtx& cx) {
   const uint64_t B = ps.B;
   const bool xt = B == 1;
   if (!xt && !(B == 32 || B == 64 || B % 128 == 0)) return fastKronKernelNotFound;
-  if (P == 64) return xt ? tc::launchOne<64, true>(ps, cx) : tc::launchOne<64, false>(ps, cx);
-  return xt ? tc::launchOne<128, true>(ps, cx) : tc::launchOne<128, false>(ps, cx);
+  if (cx.tf32 == 3) {
+    // fp32-level results from three TF32 products: 64x64 factors only (128x128 stays on the fp32 kernel)
+    if (P != 64) return fastKronKernelNotFound;
+    return xt ? tc::launchOne<64, true, true>(ps, cx) : tc::launchOne<64, false, true>(ps, cx);
+  }
+  if (P == 64) return xt ? tc::launchOne<64, true, false>(ps, cx) : tc::launchOne<64, false, false>(ps, cx);
+  return xt ? tc::launchOne<128, true, false>(ps, cx) : tc::launchOne<128, false, false>(ps, cx);
 }
+
+unsigned long long gemmTcLaunches(int split) { return tc::gLaunches[split ? 1 : 0]; }
 
 int gemmTcTimeouts() {
   int v = 0;
@@ -427,3 +505,5 @@ int gemmTcTimeouts() {
 
 // Non-zero if a bounded barrier wait of the TF32 kernel ever gave up in this process (tests).
 extern "C" int fkbGemmTcTimeouts() { return fkb::gemmTcTimeouts(); }
+// Launches of the TF32 (split = 0) or split-TF32 (split = 1) kernel by this process so far.
+extern "C" unsigned long long fkbGemmTcLaunches(int split) { return fkb::gemmTcLaunches(split); }

@@ -35,8 +35,9 @@ struct LaunchCtx {
   // Gemm launcher only: input rows split as [outer][chunk][pSplit][B] (see GemmArgs)
   unsigned pSplit = 0;
   unsigned long long pOuter = 0, nStride = 0;
-  // Gemm launcher: opt-in TF32 tensor-core kernel for fp32 passes (fastKronOptionsTF32)
-  bool tf32 = false;
+  // Gemm launcher: opt-in tensor-core kernels for fp32 passes: 0 off, 1 TF32 operands
+  // (fastKronOptionsTF32), 3 split TF32 with fp32-level results (fastKronOptionsTF32x3)
+  int tf32 = 0;
   // Strided batch in ONE launch (the reference batches in grid.z, src/kernels/gpu_kmmkernel.h:124-144):
   // entry e of `batch` reads src + e*bsX, writes dst + e*bsZ, uses Y + e*bsY and factor k at
   // F[k] + e*bsF[k] (element strides; 0 = shared).  Honoured by the generic, any-shape and

@@ -228,6 +228,46 @@ static const StreamMemOps& streamMemOps() {
   return ops;
 }
 
+// ---- staged blocks moved by a kernel ------------------------------------------------------------
+// One launch per exchange: for each of n destinations a dense [rows][width] block of the local
+// staging area goes to rows of pitch dpitch in that destination's memory (peer stores; 16-byte
+// vectors).  A thread carries one vector per destination at a time, so the traffic of an
+// exchange is spread over all peers all the time.  No waiting inside: ordering stays with the
+// stream (events or sequence flags written after the launch).
+struct MgCopyArgs {
+  const float* src[kMaxParts];
+  float* dst[kMaxParts];
+  int n = 0;
+  unsigned long long rows = 0, width = 0, dpitch = 0;      // elements
+};
+
+__global__ void __launch_bounds__(256) mgCopyKernel(const MgCopyArgs a) {
+  const unsigned long long w4 = a.width / 4, p4 = a.dpitch / 4, total = a.rows * w4;
+  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+  for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    unsigned long long o = i;
+    if (a.rows > 1) { const unsigned long long r = i / w4; o = r * p4 + (i - r * w4); }
+    float4 v[kMaxParts];
+#pragma unroll
+    for (int d = 0; d < kMaxParts; d++)
+      if (d < a.n) v[d] = __ldcs(reinterpret_cast<const float4*>(a.src[d]) + i);
+#pragma unroll
+    for (int d = 0; d < kMaxParts; d++)
+      if (d < a.n) reinterpret_cast<float4*>(a.dst[d])[o] = v[d];
+  }
+}
+
+static bool mgCopyKernelOk(const MgCopyArgs& a) {
+  if (a.n < 1 || a.n > kMaxParts || a.rows == 0 || a.width == 0 || a.width % 4 || a.dpitch % 4) return false;
+  for (int d = 0; d < a.n; d++)
+    if ((((uintptr_t)a.src[d]) | ((uintptr_t)a.dst[d])) & 15) return false;
+  return true;
+}
+static fastKronError mgCopyLaunch(const MgCopyArgs& a, int ctas, cudaStream_t s) {
+  mgCopyKernel<<<ctas, 256, 0, s>>>(a);
+  return cudaToFk(cudaGetLastError());
+}
+
 // ---- the pipelined schedule of one rank ---------------------------------------------------
 
 // Number of row slices: FASTKRON_MG_PARTS when set (a supported knob), else by the size of the
@@ -266,8 +306,12 @@ struct MgPipe {
   cudaStream_t compute = nullptr;
   // side streams of the transport: a slice's copies are spread over them by destination, so
   // several copy engines (and NVLink paths to different peers) work at once
-  static constexpr int NC = 4;
-  cudaStream_t copy[NC] = {nullptr, nullptr, nullptr, nullptr};
+  static constexpr int NC = 8;            // at most; `nc` of them exist
+  int nc = 4;
+  cudaStream_t copy[NC] = {nullptr};
+  // who moves the staged blocks: the copy engines (cudaMemcpyAsync per destination) or one
+  // kernel per exchange that reads the staging area and stores to every peer (smCtas > 0)
+  int smCtas = 0;
   cudaStream_t h2d = nullptr, d2h = nullptr;
   // per slice: passes done (evC2, evC3), host block arrived (evIn); per slice and side stream:
   // this rank's outgoing copies of exchange 1 / 2 done (evX1, evX2)
@@ -306,7 +350,20 @@ static void mgPipeDestroy(MgPipe* p) {
 static fastKronError mgPipeInitStreams(MgPipe* p) {
   int lo = 0, hi = 0;
   cudaDeviceGetStreamPriorityRange(&lo, &hi);
-  for (int i = 0; i < MgPipe::NC; i++)
+  // FASTKRON_MG_COPY_STREAMS = 1..8 side streams (default 4); FASTKRON_MG_COPY=sm[:ctas] moves the
+  // staged blocks with a kernel instead of the copy engines (supported knobs)
+  if (const char* e = getenv("FASTKRON_MG_COPY_STREAMS")) {
+    const int v = atoi(e);
+    if (v >= 1 && v <= MgPipe::NC) p->nc = v;
+  }
+  if (const char* e = getenv("FASTKRON_MG_COPY")) {
+    if (!strncmp(e, "sm", 2)) {
+      p->smCtas = 48;
+      if (e[2] == ':' && atoi(e + 3) > 0) p->smCtas = atoi(e + 3);
+      if (p->smCtas > 1024) p->smCtas = 1024;
+    }
+  }
+  for (int i = 0; i < p->nc; i++)
     if (cudaStreamCreateWithPriority(&p->copy[i], cudaStreamNonBlocking, hi) != cudaSuccess) return fastKronOtherError;
   if (cudaStreamCreateWithPriority(&p->h2d, cudaStreamNonBlocking, hi) != cudaSuccess) return fastKronOtherError;
   if (cudaStreamCreateWithPriority(&p->d2h, cudaStreamNonBlocking, hi) != cudaSuccess) return fastKronOtherError;
@@ -377,7 +434,7 @@ static fastKronError mgPipeGeometry(MgPipe* p, int g, int gk, uint32_t rows, uin
 // with flags, the message towards rank d is written right after the copy to d instead.
 static fastKronError mgSignal(MgPipe* p, int phase, int slice) {
   std::vector<cudaEvent_t>& ev = phase == 0 ? p->evX1 : p->evX2;
-  for (int c = 0; c < MgPipe::NC; c++) {
+  for (int c = 0; c < p->nc; c++) {
     cudaStream_t s = p->staged ? p->copy[c] : p->compute;
     if (cudaEventRecord(ev[(size_t)slice * MgPipe::NC + c], s) != cudaSuccess) return fastKronOtherError;
     if (!p->staged) break;                 // one stream only: event 0 stands for the slice
@@ -386,7 +443,7 @@ static fastKronError mgSignal(MgPipe* p, int phase, int slice) {
 }
 static fastKronError mgWaitEvents(MgPipe* q, int phase, int slice, cudaStream_t s) {
   const std::vector<cudaEvent_t>& ev = phase == 0 ? q->evX1 : q->evX2;
-  for (int c = 0; c < (q->staged ? MgPipe::NC : 1); c++)
+  for (int c = 0; c < (q->staged ? q->nc : 1); c++)
     if (cudaStreamWaitEvent(s, ev[(size_t)slice * MgPipe::NC + c], 0) != cudaSuccess) return fastKronOtherError;
   return fastKronSuccess;
 }
@@ -440,22 +497,36 @@ static fastKronError mgEnqueueP1(MgPipe* p, int s, const float* x, const float* 
   if (cudaEventRecord(p->evC2[s], p->compute) != cudaSuccess) return fastKronOtherError;
   if (p->staged) {
     if (p->trace) cudaEventRecord(p->trBegin[s], p->compute);
-    for (int c = 0; c < MgPipe::NC; c++)
+    for (int c = 0; c < p->nc; c++)
       if (cudaStreamWaitEvent(p->copy[c], p->evC2[s], 0) != cudaSuccess) return fastKronOtherError;
+    MgCopyArgs ca;
     for (int k = 1; k < G; k++) {
       const int d = (g + k) % G;
-      cudaStream_t cs = p->copy[(k + s) % MgPipe::NC];
-      float* dst = (float*)p->recvPeer[d] + (size_t)s * p->recvSlice + (size_t)g * p->blk1;
-      if (cudaMemcpyAsync(dst, bases[d], p->blk1 * sizeof(float), cudaMemcpyDeviceToDevice, cs) != cudaSuccess)
-        return fastKronOtherError;
-      if ((err = mgFlagTo(p, 0, s, d, cs)) != fastKronSuccess) return err;
+      ca.src[k - 1] = (const float*)bases[d];
+      ca.dst[k - 1] = (float*)p->recvPeer[d] + (size_t)s * p->recvSlice + (size_t)g * p->blk1;
+    }
+    ca.n = G - 1; ca.rows = 1; ca.width = p->blk1; ca.dpitch = p->blk1;
+    if (p->smCtas > 0 && mgCopyKernelOk(ca)) {
+      // one kernel for all destinations, exchanges of successive slices on alternating streams
+      cudaStream_t cs = p->copy[s % p->nc];
+      if ((err = mgCopyLaunch(ca, p->smCtas, cs)) != fastKronSuccess) return err;
+      for (int k = 1; k < G; k++)
+        if ((err = mgFlagTo(p, 0, s, (g + k) % G, cs)) != fastKronSuccess) return err;
+    } else {
+      for (int k = 1; k < G; k++) {
+        const int d = (g + k) % G;
+        cudaStream_t cs = p->copy[(k + s) % p->nc];
+        if (cudaMemcpyAsync(ca.dst[k - 1], ca.src[k - 1], p->blk1 * sizeof(float), cudaMemcpyDeviceToDevice, cs) != cudaSuccess)
+          return fastKronOtherError;
+        if ((err = mgFlagTo(p, 0, s, d, cs)) != fastKronSuccess) return err;
+      }
     }
   } else {
     for (int k = 1; k < G; k++)
       if ((err = mgFlagTo(p, 0, s, (g + k) % G, p->compute)) != fastKronSuccess) return err;
   }
   if (p->trace && p->staged)
-    for (int c = 0; c < MgPipe::NC; c++) cudaEventRecord(p->trEnd[(size_t)s * MgPipe::NC + c], p->copy[c]);
+    for (int c = 0; c < p->nc; c++) cudaEventRecord(p->trEnd[(size_t)s * MgPipe::NC + c], p->copy[c]);
   return mgSignal(p, 0, s);
 }
 
@@ -474,17 +545,29 @@ static fastKronError mgEnqueueP2(MgPipe* p, int s, const float* F0) {
     if (err != fastKronSuccess) return err;
     if (cudaEventRecord(p->evC3[s], p->compute) != cudaSuccess) return fastKronOtherError;
     if (p->trace) cudaEventRecord(p->trBegin[(size_t)p->parts + s], p->compute);
-    for (int c = 0; c < MgPipe::NC; c++)
+    for (int c = 0; c < p->nc; c++)
       if (cudaStreamWaitEvent(p->copy[c], p->evC3[s], 0) != cudaSuccess) return fastKronOtherError;
     const size_t rows = (size_t)r.M * q1loc, width = p->B2 * sizeof(float), dpitch = (size_t)G * width;
+    MgCopyArgs ca;
     for (int k = 0; k < G; k++) {
       const int d = (g + k) % G;
-      cudaStream_t cs = p->copy[(k + s) % MgPipe::NC];
-      float* dst = (float*)p->resultPeer[d] + resSlice + (size_t)g * p->B2;
-      if (cudaMemcpy2DAsync(dst, dpitch, st2 + (size_t)d * p->blk2, width, width, rows, cudaMemcpyDeviceToDevice,
-                            cs) != cudaSuccess)
-        return fastKronOtherError;
-      if (d != g && (err = mgFlagTo(p, 1, s, d, cs)) != fastKronSuccess) return err;
+      ca.src[k] = st2 + (size_t)d * p->blk2;
+      ca.dst[k] = (float*)p->resultPeer[d] + resSlice + (size_t)g * p->B2;
+    }
+    ca.n = G; ca.rows = rows; ca.width = p->B2; ca.dpitch = (size_t)G * p->B2;
+    if (p->smCtas > 0 && mgCopyKernelOk(ca)) {
+      cudaStream_t cs = p->copy[(s + 1) % p->nc];
+      if ((err = mgCopyLaunch(ca, p->smCtas, cs)) != fastKronSuccess) return err;
+      for (int k = 1; k < G; k++)
+        if ((err = mgFlagTo(p, 1, s, (g + k) % G, cs)) != fastKronSuccess) return err;
+    } else {
+      for (int k = 0; k < G; k++) {
+        const int d = (g + k) % G;
+        cudaStream_t cs = p->copy[(k + s) % p->nc];
+        if (cudaMemcpy2DAsync(ca.dst[k], dpitch, ca.src[k], width, width, rows, cudaMemcpyDeviceToDevice, cs) != cudaSuccess)
+          return fastKronOtherError;
+        if (d != g && (err = mgFlagTo(p, 1, s, d, cs)) != fastKronSuccess) return err;
+      }
     }
   } else {
     void* res[kMaxParts];
@@ -495,7 +578,7 @@ static fastKronError mgEnqueueP2(MgPipe* p, int s, const float* F0) {
       if ((err = mgFlagTo(p, 1, s, (g + k) % G, p->compute)) != fastKronSuccess) return err;
   }
   if (p->trace && p->staged)
-    for (int c = 0; c < MgPipe::NC; c++)
+    for (int c = 0; c < p->nc; c++)
       cudaEventRecord(p->trEnd[((size_t)p->parts + s) * MgPipe::NC + c], p->copy[c]);
   return mgSignal(p, 1, s);
 }
@@ -960,7 +1043,7 @@ int fkbMgPipeTraceGet(void* pipe, double* out, int maxExchanges) {
   int n = 0;
   for (int e = 0; e < 2 * p->parts && n < maxExchanges; e++, n++) {
     float worst = 0.f;
-    for (int c = 0; c < MgPipe::NC; c++) {
+    for (int c = 0; c < p->nc; c++) {
       float ms = 0.f;
       if (cudaEventElapsedTime(&ms, p->trBegin[e], p->trEnd[(size_t)e * MgPipe::NC + c]) != cudaSuccess) { cudaGetLastError(); ms = 0.f; }
       if (ms > worst) worst = ms;

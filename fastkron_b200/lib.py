@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libFastKron.so")
 OP_N, OP_T = 1, 2
 BACKEND_NONE, BACKEND_X86, BACKEND_ARM, BACKEND_CUDA, BACKEND_HIP = 1, 2, 4, 8, 16
 OPT_NONE, OPT_USE_FUSION, OPT_TUNE = 1, 2, 4
+OPT_TF32, OPT_TF32X3 = 8, 16          # not in the reference: tensor-core opt-ins for fp32 large factors
 (SUCCESS, BACKEND_NOT_AVAILABLE, INVALID_MEMORY_ACCESS, KERNEL_NOT_FOUND, INVALID_ARGUMENT,
  INVALID_KMM_PROBLEM, OTHER_ERROR) = range(7)
 
@@ -52,6 +53,7 @@ def load():
     lib.fastKronGetErrorString.restype = ctypes.c_char_p
     lib.fastKronGetBackends.restype = ctypes.c_uint32
     lib.fastKronDestroy.restype = None
+    lib.fkbGemmTcLaunches.restype = ctypes.c_ulonglong
     return lib
 
 

@@ -62,7 +62,13 @@ enum fastKronOptions {
    * tensor cores (operands read with a 10-bit mantissa, fp32 accumulation); results then
    * agree with fp32 only to a few 1e-3 of the row maximum.  Also switched on by the
    * environment variable FASTKRON_TF32=1.  Off by default. */
-  fastKronOptionsTF32      = 1 << 3
+  fastKronOptionsTF32      = 1 << 3,
+  /* Not in the reference.  Opt-in: fp32 passes with 64x64 factors run on the tensor cores with
+   * every operand split into two TF32 numbers and three products per fp32 product (fp32
+   * accumulation); results agree with the default fp32 kernels to about 1e-6 of the row
+   * maximum.  Also switched on by FASTKRON_TF32=3.  Off by default; wins over TF32 when both
+   * are set. */
+  fastKronOptionsTF32x3    = 1 << 4
 };
 
 /* reference: include/fastkron.h:74-82 */

@@ -133,11 +133,14 @@ def test_fusion_off_matches_fusion_on(h):
 
 @pytest.mark.parametrize("mm", ["mkm", "kmm"])
 @pytest.mark.parametrize("dt", ["f32", "f64"])
-def test_forward_intermediates(h, mm, dt):
-    """{s,d}{mkm,kmm}Forward: Z and each of the N-1 intermediates in the reference's layout."""
+@pytest.mark.parametrize("ps,qs,M", [([4, 3, 8, 2], [2, 5, 8, 3], 6), ([16, 12, 8], [16, 10, 24], 37),
+                                     ([32, 16], [32, 16], 64)], ids=["tiny", "narrow-tiles", "pow2"])
+def test_forward_intermediates(h, mm, dt, ps, qs, M):
+    """{s,d}{mkm,kmm}Forward: Z and each of the N-1 intermediates in the reference's layout
+    (tiny factors: one thread per output; the others: the any-shape kernel's 16- and 32-wide tiles)."""
     import torch
     import gpu_util
-    c = cases.case(mm, dt, 6, [4, 3, 8, 2], [2, 5, 8, 3], seed=77)
+    c = cases.case(mm, dt, M, ps, qs, seed=77)
     x, fs, _ = cases.operands(c)
     zo, inter_o = oracle.port_gekmm(mm, x, fs, c["ps"], c["qs"], c["M"], want_intermediates=True)
     ye, ies = h.sizes_forward(c["M"], c["ps"], c["qs"])

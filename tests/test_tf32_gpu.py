@@ -78,3 +78,41 @@ def test_tf32_is_off_by_default():
         assert cases.row_rel_err(z, want, c["mm"]) <= cases.TOL["f32"]
     finally:
         hd.close()
+
+
+# ---- split TF32 (fastKronOptionsTF32x3): three tensor-core products per fp32 product -----------
+
+TF32X3_TOL = 1e-5      # of the row maximum; observed a few 1e-7 to 2e-6
+OPT_TF32X3 = 16
+
+X3_CASES = [
+    cases.case("mkm", "f32", 16, [32, 64], [32, 64], seed=931),                  # contraction index contiguous
+    cases.case("mkm", "f32", 3, [32, 64], [32, 64], seed=932),                   # ragged tile
+    cases.case("mkm", "f32", 6, [64, 32], [64, 32], seed=933),                   # trailing extent 32
+    cases.case("mkm", "f32", 5, [64, 64], [64, 64], seed=934),                   # trailing extent 64 and 1
+    cases.case("mkm", "f32", 4, [64, 16, 8], [64, 16, 8], seed=935),             # trailing extent 128
+    cases.case("mkm", "f32", 4, [64, 64, 64], [64, 64, 64], seed=936),
+    cases.case("mkm", "f32", 8, [64, 64], [64, 64], "N", "T", 2.0, 0.5, seed=937),
+    cases.case("kmm", "f32", 128, [64, 64], [64, 64], "N", "N", 1.5, 1.0, seed=938),
+    cases.case("mkm", "f32", 40, [64, 64, 64], [64, 64, 64], seed=939),          # several tiles per CTA: ring wraps
+]
+
+
+@pytest.mark.parametrize("c", X3_CASES, ids=cases.case_id)
+def test_split_tf32_option_matches_fp32(c):
+    import fastkron_b200
+    import gpu_util
+    from fastkron_b200 import lib as fk
+    hd = fastkron_b200.FastKron()
+    hd.set_options(OPT_USE_FUSION | OPT_TF32X3)
+    try:
+        before = fk.get().fkbGemmTcLaunches(1)
+        x, fs, y = cases.operands(c)
+        z = gpu_util.run_case(hd, c, x=x, fs=fs, y=y)
+        want = oracle.port_gekmm(c["mm"], x, fs, c["ps"], c["qs"], c["M"], c["opx"], c["opf"], c["alpha"], c["beta"], y)
+        err = cases.row_rel_err(z, want, c["mm"])
+        assert fk.get().fkbGemmTcTimeouts() == 0
+        assert fk.get().fkbGemmTcLaunches(1) > before, "the split tensor-core kernel did not run"
+        assert err <= TF32X3_TOL, err
+    finally:
+        hd.close()
