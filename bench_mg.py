@@ -319,7 +319,8 @@ def run(args, CONFIGS, B):
                     "copies_alone_gbs_aggregate_per_direction": M * Kl * 4 * world / (duplex_alone_ms * 1e-3) / 1e9,
                     "matches_device_result": e2e_same},
             "cpu_baseline": None, "parity_rows_max_rel_err": check,
-            "row_slices": parts, "exchange_mode": mode, "c_api_single_process": c_api,
+            "row_slices": parts, "exchange_mode": mode, "compute_lanes": int(L.fkbMgPipeLanes(eng.pipe)) if eng.pipe is not None else 1,
+            "c_api_single_process": c_api,
             "exchange": ("2 all-to-alls per step; staged: kernels fill local per-destination blocks, copy engines ship "
                          "them over NVLink; fused: the producing kernels store into the peers; ranks are ordered by "
                          "32-bit sequence flags in device memory (stream memory operations), no collective library "

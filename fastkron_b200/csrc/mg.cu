@@ -313,6 +313,12 @@ struct MgPipe {
   // kernel per exchange that reads the staging area and stores to every peer (smCtas > 0)
   int smCtas = 0;
   cudaStream_t h2d = nullptr, d2h = nullptr;
+  // fused transport with several row slices: the slices alternate between `lanes` streams, each
+  // launching on 1/lanes of the CTA slots, so that the passes of one slice that store to the
+  // peers (bound by NVLink) run beside the local passes of the next (bound by arithmetic)
+  int lanes = 1;
+  cudaStream_t lane[2] = {nullptr, nullptr};
+  cudaEvent_t evFork = nullptr, evStagger = nullptr;
   // per slice: passes done (evC2, evC3), host block arrived (evIn); per slice and side stream:
   // this rank's outgoing copies of exchange 1 / 2 done (evX1, evX2)
   std::vector<cudaEvent_t> evC2, evC3, evX1, evX2, evIn;
@@ -335,8 +341,10 @@ static void mgPipeDestroy(MgPipe* p) {
     for (cudaEvent_t e : *v) cudaEventDestroy(e);
   for (cudaStream_t s : p->copy)
     if (s) cudaStreamDestroy(s);
-  for (cudaStream_t s : {p->h2d, p->d2h})
+  for (cudaStream_t s : {p->h2d, p->d2h, p->lane[0], p->lane[1]})
     if (s) cudaStreamDestroy(s);
+  for (cudaEvent_t e : {p->evFork, p->evStagger})
+    if (e) cudaEventDestroy(e);
   if (p->owned) {
     for (float* b : {p->t1, p->t2, p->stage1, p->recv, p->result, p->xdev})
       if (b) cudaFree(b);
@@ -365,6 +373,13 @@ static fastKronError mgPipeInitStreams(MgPipe* p) {
   }
   for (int i = 0; i < p->nc; i++)
     if (cudaStreamCreateWithPriority(&p->copy[i], cudaStreamNonBlocking, hi) != cudaSuccess) return fastKronOtherError;
+  if (p->lanes > 1) {
+    for (int i = 0; i < p->lanes; i++)
+      if (cudaStreamCreateWithPriority(&p->lane[i], cudaStreamNonBlocking, lo) != cudaSuccess) return fastKronOtherError;
+    if (cudaEventCreateWithFlags(&p->evFork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&p->evStagger, cudaEventDisableTiming) != cudaSuccess)
+      return fastKronOtherError;
+  }
   if (cudaStreamCreateWithPriority(&p->h2d, cudaStreamNonBlocking, hi) != cudaSuccess) return fastKronOtherError;
   if (cudaStreamCreateWithPriority(&p->d2h, cudaStreamNonBlocking, hi) != cudaSuccess) return fastKronOtherError;
   for (auto* v : {&p->evC2, &p->evC3, &p->evX1, &p->evX2, &p->evIn}) {
@@ -402,16 +417,28 @@ static fastKronError mgPipeGeometry(MgPipe* p, int g, int gk, uint32_t rows, uin
     else if (m && !strcmp(m, "staged") && can) wantStaged = 1;
   }
   if (wantStaged == 1 && !can) return fastKronKernelNotFound;
-  // Automatic choice, from measurements on 8 B200 behind NVSwitch: with two GPUs half of every
-  // block stays local and storing straight from the kernels wins (C5: 26.3 ms against 28.6 ms);
-  // from four GPUs on, the copy engines win because the kernels then run at full speed while
-  // the NVLink traffic of another row slice is in flight.
-  if (wantStaged < 0) wantStaged = (can && gk >= 3) ? 1 : 0;
+  // Automatic choice, from measurements on 8 B200 behind NVSwitch (C5): with two GPUs half of
+  // every block stays local and storing straight from the kernels wins (25.5 ms against 28.5 ms);
+  // with four, the copy engines win (14.6 against 16.4 ms) because the kernels then run at full
+  // speed while the NVLink traffic of another row slice is in flight; with eight, seven
+  // concurrent copies per exchange only reach about 380 GB/s per GPU and the exchanges outlast
+  // the arithmetic (10.1 ms), so the kernels' own stores win again (9.6 ms).
+  if (wantStaged < 0) wantStaged = (can && gk >= 3 && gk < 8) ? 1 : 0;
   p->staged = wantStaged == 1;
-  if (!p->staged && autoParts && !getenv("FASTKRON_MG_PARTS")) {
-    p->parts = 1;
-    p->rank.M = rows;
+  // Fused transport: one slice on the compute stream, except for eight and more GPUs, where most
+  // of a pass's output crosses NVLink and two lanes (FASTKRON_MG_LANES=1|2 overrides) let the
+  // slices' NVLink-bound passes run beside the next slices' local ones (C5, 8 GPUs: 8.9 ms
+  // against 9.5 ms).
+  int wantLanes = 1;
+  if (!p->staged) {
+    const char* e = getenv("FASTKRON_MG_LANES");
+    wantLanes = e ? (atoi(e) == 2 ? 2 : 1) : (gk >= 8 ? 2 : 1);
+    if (wantLanes == 1 && autoParts && !getenv("FASTKRON_MG_PARTS")) {
+      p->parts = 1;
+      p->rank.M = rows;
+    }
   }
+  p->lanes = (wantLanes == 2 && p->parts >= 2) ? 2 : 1;
   const uint64_t B = prodQ(p->rank, 2);
   const uint64_t p1loc = Ps[0] / gk, q1loc = Qs[0] / gk, q2loc = Qs[1] / gk;
   p->B2 = q2loc * B;
@@ -427,6 +454,18 @@ static fastKronError mgPipeGeometry(MgPipe* p, int g, int gk, uint32_t rows, uin
   return fastKronSuccess;
 }
 
+// The stream that runs the kernels of slice s, and the SM count its launches size their grids for.
+static cudaStream_t mgLaneOf(const MgPipe* p, int s) { return p->lanes > 1 ? p->lane[s % p->lanes] : p->compute; }
+static int mgLaneSms(const MgPipe* p) { return p->lanes > 1 ? (p->rank.smCount + p->lanes - 1) / p->lanes : p->rank.smCount; }
+// Start of a call: the lanes continue where the caller's stream stands.
+static fastKronError mgFork(MgPipe* p) {
+  if (p->lanes <= 1) return fastKronSuccess;
+  if (cudaEventRecord(p->evFork, p->compute) != cudaSuccess) return fastKronOtherError;
+  for (int i = 0; i < p->lanes; i++)
+    if (cudaStreamWaitEvent(p->lane[i], p->evFork, 0) != cudaSuccess) return fastKronOtherError;
+  return fastKronSuccess;
+}
+
 // ---- ordering primitives --------------------------------------------------------------------
 // A slice's outgoing copies of one exchange run on the NC side streams (fused transport: there
 // are none, the kernel itself stored the rows and "side stream" means the compute stream).
@@ -435,7 +474,7 @@ static fastKronError mgPipeGeometry(MgPipe* p, int g, int gk, uint32_t rows, uin
 static fastKronError mgSignal(MgPipe* p, int phase, int slice) {
   std::vector<cudaEvent_t>& ev = phase == 0 ? p->evX1 : p->evX2;
   for (int c = 0; c < p->nc; c++) {
-    cudaStream_t s = p->staged ? p->copy[c] : p->compute;
+    cudaStream_t s = p->staged ? p->copy[c] : mgLaneOf(p, slice);
     if (cudaEventRecord(ev[(size_t)slice * MgPipe::NC + c], s) != cudaSuccess) return fastKronOtherError;
     if (!p->staged) break;                 // one stream only: event 0 stands for the slice
   }
@@ -479,7 +518,12 @@ static fastKronError mgWaitAll(MgPipe* p, int phase, int slice, cudaStream_t s) 
 static fastKronError mgEnqueueP1(MgPipe* p, int s, const float* x, const float* const* Fs) {
   const int G = p->rank.gk, g = p->rank.g;
   MgRank r = p->rank;
-  r.stream = p->compute;
+  cudaStream_t ks = mgLaneOf(p, s);
+  r.stream = ks;
+  r.smCount = mgLaneSms(p);
+  // the second lane starts half a slice late, so that its NVLink-bound passes fall beside the
+  // first lane's local ones
+  if (p->lanes > 1 && s == 1 && cudaStreamWaitEvent(ks, p->evStagger, 0) != cudaSuccess) return fastKronOtherError;
   float* t1 = p->t1 + (size_t)s * p->tmpSlice;
   float* t2 = p->t2 + (size_t)s * p->tmpSlice;
   float* recvS = (float*)p->recvPeer[g] + (size_t)s * p->recvSlice;
@@ -494,9 +538,10 @@ static fastKronError mgEnqueueP1(MgPipe* p, int s, const float* x, const float* 
   }
   fastKronError err = mgPhase1(p->eng, r, xs, Fs, t1, t2, bases, p->staged);
   if (err != fastKronSuccess) return err;
-  if (cudaEventRecord(p->evC2[s], p->compute) != cudaSuccess) return fastKronOtherError;
+  if (cudaEventRecord(p->evC2[s], ks) != cudaSuccess) return fastKronOtherError;
+  if (p->lanes > 1 && s == 0 && cudaEventRecord(p->evStagger, ks) != cudaSuccess) return fastKronOtherError;
   if (p->staged) {
-    if (p->trace) cudaEventRecord(p->trBegin[s], p->compute);
+    if (p->trace) cudaEventRecord(p->trBegin[s], ks);
     for (int c = 0; c < p->nc; c++)
       if (cudaStreamWaitEvent(p->copy[c], p->evC2[s], 0) != cudaSuccess) return fastKronOtherError;
     MgCopyArgs ca;
@@ -523,7 +568,7 @@ static fastKronError mgEnqueueP1(MgPipe* p, int s, const float* x, const float* 
     }
   } else {
     for (int k = 1; k < G; k++)
-      if ((err = mgFlagTo(p, 0, s, (g + k) % G, p->compute)) != fastKronSuccess) return err;
+      if ((err = mgFlagTo(p, 0, s, (g + k) % G, ks)) != fastKronSuccess) return err;
   }
   if (p->trace && p->staged)
     for (int c = 0; c < p->nc; c++) cudaEventRecord(p->trEnd[(size_t)s * MgPipe::NC + c], p->copy[c]);
@@ -533,8 +578,10 @@ static fastKronError mgEnqueueP1(MgPipe* p, int s, const float* x, const float* 
 static fastKronError mgEnqueueP2(MgPipe* p, int s, const float* F0) {
   const int G = p->rank.gk, g = p->rank.g;
   MgRank r = p->rank;
-  r.stream = p->compute;
-  fastKronError err = mgWaitAll(p, 0, s, p->compute);
+  cudaStream_t ks = mgLaneOf(p, s);
+  r.stream = ks;
+  r.smCount = mgLaneSms(p);
+  fastKronError err = mgWaitAll(p, 0, s, ks);
   if (err != fastKronSuccess) return err;
   const float* recvS = (const float*)p->recvPeer[g] + (size_t)s * p->recvSlice;
   const uint64_t q1loc = p->Qs[0] / G;
@@ -543,8 +590,8 @@ static fastKronError mgEnqueueP2(MgPipe* p, int s, const float* F0) {
     float* st2 = p->t1 + (size_t)s * p->tmpSlice;               // free again: every local pass of the slice is done
     err = mgPhase2Staged(p->eng, r, recvS, F0, st2);
     if (err != fastKronSuccess) return err;
-    if (cudaEventRecord(p->evC3[s], p->compute) != cudaSuccess) return fastKronOtherError;
-    if (p->trace) cudaEventRecord(p->trBegin[(size_t)p->parts + s], p->compute);
+    if (cudaEventRecord(p->evC3[s], ks) != cudaSuccess) return fastKronOtherError;
+    if (p->trace) cudaEventRecord(p->trBegin[(size_t)p->parts + s], ks);
     for (int c = 0; c < p->nc; c++)
       if (cudaStreamWaitEvent(p->copy[c], p->evC3[s], 0) != cudaSuccess) return fastKronOtherError;
     const size_t rows = (size_t)r.M * q1loc, width = p->B2 * sizeof(float), dpitch = (size_t)G * width;
@@ -575,7 +622,7 @@ static fastKronError mgEnqueueP2(MgPipe* p, int s, const float* F0) {
     err = mgPhase2(p->eng, r, recvS, F0, res);
     if (err != fastKronSuccess) return err;
     for (int k = 1; k < G; k++)
-      if ((err = mgFlagTo(p, 1, s, (g + k) % G, p->compute)) != fastKronSuccess) return err;
+      if ((err = mgFlagTo(p, 1, s, (g + k) % G, ks)) != fastKronSuccess) return err;
   }
   if (p->trace && p->staged)
     for (int c = 0; c < p->nc; c++)
@@ -792,6 +839,8 @@ fastKronError fastKronMgSGEMM(fastKronHandle handle, const uint32_t NumKronMats,
           p->recvPeer[d] = (float*)temp1[row * mg->gk + d] + half;
           p->resultPeer[d] = result[row * mg->gk + d];
         }
+        cudaSetDevice(mg->device[g]);
+        if (err == fastKronSuccess) err = mgFork(p);
       }
       std::vector<std::pair<int, int>> order;
       mgOrder(mg->pipes[0]->parts, &order);
@@ -920,6 +969,9 @@ fastKronError fkbMgPipeCreate(fastKronHandle handle, int rank, int world, uint32
   return fastKronSuccess;
 }
 
+// Compute lanes of a pipe (1, or 2 for the fused transport on eight and more GPUs).
+int fkbMgPipeLanes(void* pipe) { return pipe ? reinterpret_cast<MgPipe*>(pipe)->lanes : 0; }
+
 fastKronError fkbMgPipeLocalBuffers(void* pipe, void** recv, size_t* recvBytes, void** result, size_t* resultBytes,
                                     void** flags, size_t* flagBytes, int* parts, int* staged) {
   MgPipe* p = reinterpret_cast<MgPipe*>(pipe);
@@ -981,12 +1033,13 @@ static fastKronError mgPipeRun(MgPipe* p, const float* x, const float* const Fs[
         return fastKronOtherError;
     }
   }
+  if ((err = mgFork(p)) != fastKronSuccess) return err;
   std::vector<std::pair<int, int>> order;
   mgOrder(p->parts, &order);
   for (size_t o = 0; o < order.size() && err == fastKronSuccess; o++) {
     const int s = order[o].second;
     if (order[o].first == 1) {
-      if (hostX && cudaStreamWaitEvent(p->compute, p->evIn[s], 0) != cudaSuccess) return fastKronOtherError;
+      if (hostX && cudaStreamWaitEvent(mgLaneOf(p, s), p->evIn[s], 0) != cudaSuccess) return fastKronOtherError;
       err = mgEnqueueP1(p, s, x, Fs);
     } else {
       err = mgEnqueueP2(p, s, Fs[0]);

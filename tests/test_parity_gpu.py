@@ -134,7 +134,8 @@ def test_fusion_off_matches_fusion_on(h):
 @pytest.mark.parametrize("mm", ["mkm", "kmm"])
 @pytest.mark.parametrize("dt", ["f32", "f64"])
 @pytest.mark.parametrize("ps,qs,M", [([4, 3, 8, 2], [2, 5, 8, 3], 6), ([16, 12, 8], [16, 10, 24], 37),
-                                     ([32, 16], [32, 16], 64)], ids=["tiny", "narrow-tiles", "pow2"])
+                                     ([32, 16], [32, 16], 64), ([16, 3, 8], [16, 5, 8], 5), ([8] * 4, [8] * 4, 33)],
+                         ids=["tiny", "narrow-tiles", "pow2", "pow2-ragged", "pow2-many-rows"])
 def test_forward_intermediates(h, mm, dt, ps, qs, M):
     """{s,d}{mkm,kmm}Forward: Z and each of the N-1 intermediates in the reference's layout
     (tiny factors: one thread per output; the others: the any-shape kernel's 16- and 32-wide tiles)."""
