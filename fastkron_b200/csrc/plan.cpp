@@ -185,7 +185,7 @@ fastKronError makePlan(const Problem& pr, const PlanOptions& optIn, Plan* out) {
         if (gemmEligible(pr.dt, P, Q, Bg)) ps.kind = KernelKind::Gemm;
       }
       if (ps.kind == KernelKind::Generic && !opt.forceGeneric && gemmAnyEligible(P, Q)) {
-        // every other shape with a factor of 64 elements or more: the any-shape kernel (variant 3),
+        // every other shape the eligibility rule admits (64 elements or more, or at least 5x5): the any-shape kernel (variant 3),
         // whatever the strides, the alignment or the orientations of input and result
         ps.kind = KernelKind::Gemm;
         ps.variant = 3;
