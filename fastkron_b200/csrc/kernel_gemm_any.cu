@@ -48,6 +48,9 @@ struct AnyArgs {
   T alpha, beta;
   int epilogue;
   int vecX, vecZ, vecF;                  // 16-byte accesses allowed on X / on Z and Y / on F rows
+  int vecZJ;                             // [j][p] staging only: the output is contiguous along the chunk index
+                                         // (zsA == 1, the rotating layout of the forward variants): 16-byte
+                                         // stores along j after a transposition through shared memory
   // strided batch: tile index = entry * tilesPerEntry + tile within the entry (a tile never spans entries)
   unsigned batch;
   unsigned long long tilesPerEntry, bsX, bsZ, bsY, bsF;
@@ -76,6 +79,8 @@ struct AnyCfg {
   static constexpr int XELEMS = XELEMS_T > XELEMS_N ? XELEMS_T : XELEMS_N;
   static constexpr int FELEMS = PC * TQ;
   static constexpr size_t SMEM = 2 * (size_t)(XELEMS + FELEMS) * sizeof(T);
+  // the [j][p] variant may park a finished [TQ][TJ + VEC] tile in the two X buffers
+  static_assert(TQ * (TJ + VEC) <= 2 * XELEMS, "output tile fits the X buffers");
 };
 
 // Address pieces of trailing position J: chunk (m, a) and b.
@@ -315,6 +320,40 @@ __global__ void __launch_bounds__(128, 3) gemmAnyKernel(const AnyArgs<T> a0) {
           }
         }
       }
+    } else if (a.vecZJ) {
+      // the loop's last barrier is behind every thread: the X buffers are free; park the tile
+      // there as [q][j] and write rows of it with 16-byte stores along j
+      constexpr int LDO = TJ + VEC;
+      T* ot = Xs;
+#pragma unroll
+      for (int qi = 0; qi < MQ; qi++) {
+        const int ql = (qi / VEC) * QS + tq * VEC + (qi % VEC);
+#pragma unroll
+        for (int ji = 0; ji < MJ; ji++) ot[ql * LDO + tj + ji * JT] = acc[qi][ji];
+      }
+      __syncthreads();
+      constexpr int VPR = TJ / VEC;
+      for (int idx = tid; idx < TQ * VPR; idx += THREADS) {
+        const int ql = idx / VPR, jv = (idx % VPR) * VEC;
+        const unsigned long long J = J0 + (unsigned)jv;
+        const unsigned q = q0 + (unsigned)ql;
+        if (J >= a.Jtotal || q >= a.Q) continue;            // A % VEC == 0: vectors are whole and stay in one row
+        unsigned long long m, ac, b;
+        splitJ(a, J, m, ac, b);
+        const long long off = (long long)m * a.zsM + (long long)ac + (long long)q * a.zsG;
+        V o = *reinterpret_cast<const V*>(ot + ql * LDO + jv);
+        if (epi) {
+#pragma unroll
+          for (int e = 0; e < VEC; e++) o.v[e] = a.alpha * o.v[e];
+          if (useY) {
+            const V y = *reinterpret_cast<const V*>(a.Y + off);
+#pragma unroll
+            for (int e = 0; e < VEC; e++) o.v[e] = fma(a.beta, y.v[e], o.v[e]);
+          }
+        }
+        *reinterpret_cast<V*>(a.Z + off) = o;
+      }
+      // (the next tile's table fill ends in a barrier before any thread refills the X buffers)
     } else {
 #pragma unroll
       for (int ji = 0; ji < MJ; ji++) {
@@ -391,6 +430,7 @@ static fastKronError launchGemmAnyT(const Pass& ps, const LaunchCtx& cx) {
   a.zsM = ps.zsM; a.zsA = ps.zsA; a.zsG = ps.zsG; a.zsB = ps.zsB;
   a.Jtotal = ps.M * ps.A * ps.B;
   a.alpha = (T)cx.alpha; a.beta = (T)cx.beta; a.epilogue = ps.epilogue ? 1 : 0;
+  a.vecZJ = 0;
   if (a.Jtotal == 0) return fastKronSuccess;
   a.qTiles = (a.Q + C::TQ - 1) / C::TQ;
   a.tilesPerEntry = (unsigned long long)a.qTiles * ((a.Jtotal + C::TJ - 1) / C::TJ);
@@ -409,11 +449,16 @@ static fastKronError launchGemmAnyT(const Pass& ps, const LaunchCtx& cx) {
     a.vecX = mult((long long)a.P, VEC) && mult(ps.xsM, VEC) && mult(ps.xsA, VEC) && al16(a.X);
     a.vecZ = ps.zsG == 1 && mult((long long)a.Q, VEC) && mult(ps.zsM, VEC) && mult(ps.zsA, VEC) && al16(a.Z) &&
              (a.Y == nullptr || al16(a.Y));
+    // (fp32 only: measured on B200, 16x16^4 forward 0.90 -> 0.72 ms, 8x8^6 5.0 -> 3.4 ms; fp64 scalar stores
+    // already make 64-byte runs per quarter warp and showed no gain from the shared-memory round trip)
+    a.vecZJ = sizeof(T) == 4 && !a.vecZ && ps.zsA == 1 && mult((long long)ps.A, VEC) && mult(ps.zsM, VEC) && mult(ps.zsG, VEC) && al16(a.Z) &&
+              (a.Y == nullptr || al16(a.Y));
   }
   a.vecF = cx.fsQ == 1 && mult((long long)a.Q, VEC) && mult(cx.fsP, VEC) && al16(a.F);
   if (a.batch > 1) {
     a.vecX = a.vecX && mult((long long)a.bsX, VEC);
     a.vecZ = a.vecZ && mult((long long)a.bsZ, VEC) && mult((long long)a.bsY, VEC);
+    a.vecZJ = a.vecZJ && mult((long long)a.bsZ, VEC) && mult((long long)a.bsY, VEC);
     a.vecF = a.vecF && mult((long long)a.bsF, VEC);
   }
 
