@@ -171,6 +171,12 @@ def test_plan_fuses_benchmark_shapes(L):
     assert n == 3 and all(" gemm " in ln for ln in lines)
     n, lines = describe(L, "mkm", "f32", 16, [4] * 3, [4] * 3, align=4)
     assert n == 3 and all(" generic " in ln for ln in lines)
+    # factors from 5x5 on go to the any-shape kernel (narrow tiles); smaller ones and factors with a
+    # side below 5 and fewer than 64 elements stay with the one-thread-per-output kernel
+    for p, q, kind in ((5, 5, "gemm"), (7, 6, "gemm"), (3, 3, "generic"), (2, 12, "generic"), (12, 2, "generic"),
+                       (2, 32, "gemm"), (4, 16, "gemm"), (6, 4, "generic")):
+        n, lines = describe(L, "mkm", "f64", 8, [p, p], [q, q])
+        assert n == 2 and all(" %s " % kind in ln for ln in lines), (p, q, lines)
 
 
 def test_no_large_factor_pass_is_left_to_the_one_thread_per_output_kernel(L):
